@@ -61,6 +61,8 @@ class LayerSpec:
     arrangement: str = "pre_norm"
     names: Tuple[Tuple[str, str], ...] = ()
     token_input: Optional[PartSpec] = None      # a sublayer that reads the token ids again (arrangements that take one)
+    out_norm: Optional[PartSpec] = None         # a norm on every sublayer's output before it joins the stream (arrangements that take one)
+    layer_scale: bool = False                   # a learned vector per sublayer multiplies what joins the stream
 
     def name_of(self, role: str) -> str:
         for key, value in self.names:

@@ -68,7 +68,8 @@ __global__ void __launch_bounds__(256)
 qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                  const int* __restrict__ positions, const int* __restrict__ slot_mapping, int64_t num_slots,
                  int page_size, int nq, int nkv, int dk, int dv, float temp_coef, int temp_every, unsigned* status,
-                 const float* __restrict__ freq, int rot_half) {
+                 const float* __restrict__ freq, int rot_half, float magnitude, const T* __restrict__ v_first,
+                 int64_t v_first_stride, float v_mix) {
   extern __shared__ float turn[];            // [2 * rot_half]: cosines, then sines, of this token's angles
   pdl_wait();
   pdl_launch_dependents();
@@ -81,8 +82,8 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
     const float p = (float)positions[t];
     for (int i = threadIdx.x; i < rot_half; i += blockDim.x) {
       const float angle = p * freq[i];
-      turn[i] = cosf(angle);
-      turn[rot_half + i] = sinf(angle);
+      turn[i] = cosf(angle) * magnitude;
+      turn[rot_half + i] = sinf(angle) * magnitude;
     }
     __syncthreads();
   }
@@ -146,9 +147,26 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
       const int g = i / k8, c = i % k8;
       reinterpret_cast<uint4*>(k_cache + ((page * nkv + g) * page_size + offset) * dk)[c] = turned_word(src + wq / 8, i, 1.f);
     }
+    const bool mix_words = v_first != nullptr && v_first_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(v_first) & 15) == 0;
     for (int i = threadIdx.x; i < wv / 8; i += blockDim.x) {
       const int g = i / v8, c = i % v8;
-      reinterpret_cast<uint4*>(v_cache + ((page * nkv + g) * page_size + offset) * dv)[c] = src[(wq + wk) / 8 + i];
+      uint4 raw = src[(wq + wk) / 8 + i];
+      if (mix_words) {
+        const uint4 other = reinterpret_cast<const uint4*>(v_first + (int64_t)t * v_first_stride)[i];
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+        const __nv_bfloat162* o = reinterpret_cast<const __nv_bfloat162*>(&other);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 x = __bfloat1622float2(p[e]), y = __bfloat1622float2(o[e]);
+          p[e] = __floats2bfloat162_rn((1.f - v_mix) * x.x + v_mix * y.x, (1.f - v_mix) * x.y + v_mix * y.y);
+        }
+      } else if (v_first != nullptr) {
+        bf16* p = reinterpret_cast<bf16*>(&raw);
+        for (int e = 0; e < 8; ++e)
+          p[e] = __float2bfloat16_rn((1.f - v_mix) * __bfloat162float(p[e]) +
+                                     v_mix * to_f32(v_first[(int64_t)t * v_first_stride + i * 8 + e]));
+      }
+      reinterpret_cast<uint4*>(v_cache + ((page * nkv + g) * page_size + offset) * dv)[c] = raw;
     }
     return;
   }
@@ -158,7 +176,9 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
   }
   for (int i = threadIdx.x; i < wv; i += blockDim.x) {
     const int g = i / dv, c = i % dv;
-    v_cache[((page * nkv + g) * page_size + offset) * dv + c] = row[wq + wk + i];
+    T v = row[wq + wk + i];
+    if (v_first != nullptr) v = from_f32<T>((1.f - v_mix) * to_f32(v) + v_mix * to_f32(v_first[(int64_t)t * v_first_stride + i]));
+    v_cache[((page * nkv + g) * page_size + offset) * dv + c] = v;
   }
 }
 
@@ -333,7 +353,8 @@ attention_sink_merge_kernel(const float* __restrict__ partial, int segments, T* 
 VOSTI_API int vosti_qkv_store(const void* qkv, void* q_out, void* k_cache, void* v_cache, const int* positions,
                               const int* slot_mapping, int64_t num_slots, int page_size, int tokens, int nq, int nkv,
                               int dk, int dv, float temp_coef, int temp_every, int is_f32, unsigned* status,
-                              const float* freq, int rot_half, cudaStream_t stream) {
+                              const float* freq, int rot_half, float magnitude, const void* v_first, int64_t v_first_stride,
+                              float v_mix, cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv >= 0 && dk > 0 && dv > 0, "qkv_store: bad sizes");
   VOSTI_REQUIRE(temp_coef == 0.f || (temp_every > 0 && positions != nullptr), "qkv_store: the temperature needs positions and a positive period");
   VOSTI_REQUIRE(k_cache == nullptr || (v_cache != nullptr && slot_mapping != nullptr && page_size > 0), "qkv_store: a cache needs slots");
@@ -344,11 +365,11 @@ VOSTI_API int vosti_qkv_store(const void* qkv, void* q_out, void* k_cache, void*
   if (is_f32)
     vosti_launch(qkv_store_kernel<float>, dim3(tokens), dim3(256), turn_bytes, stream, (const float*)qkv, (float*)q_out, (float*)k_cache,
                  (float*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, dk, dv, temp_coef, temp_every, status, freq,
-                 rot_half);
+                 rot_half, magnitude, (const float*)v_first, v_first_stride, v_mix);
   else
     vosti_launch(qkv_store_kernel<bf16>, dim3(tokens), dim3(256), turn_bytes, stream, (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
                  (bf16*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, dk, dv, temp_coef, temp_every, status, freq,
-                 rot_half);
+                 rot_half, magnitude, (const bf16*)v_first, v_first_stride, v_mix);
   VOSTI_LAUNCH_CHECK();
 }
 

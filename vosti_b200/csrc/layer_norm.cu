@@ -1,0 +1,101 @@
+// Layer norm (mean and variance, weight and bias) over a float32 residual stream, for blocks
+// that also norm and scale what a sublayer returns before it joins the stream:
+//
+//   y given, with (wy, by, sy):   t = ((y - mean y) / sqrt(var y + eps_y) * wy + by) * sy
+//   y given, plain:               t = y
+//   x = stream + t                (stream absent: x = t)      -> stream_out (float32)
+//   out = (x - mean x) / sqrt(var x + eps) * w + b            -> out (serving type or float32)
+//
+// so that one launch serves "norm the sublayer's output, scale it, add it, norm the sum for the
+// next sublayer". The variance is the mean of the squared deviations, taken in a second walk
+// over the row after the mean is known; the row lives in shared memory between the walks. All
+// arithmetic is float32; reductions have a fixed order that depends on the width only.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float2 mean_inv(const float* row, int width, float eps, float* scratch) {
+  float s = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) s += row[i];
+  const float mean = block_sum(s, scratch) / (float)width;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float d = row[i] - mean;
+    q = fmaf(d, d, q);
+  }
+  const float var = block_sum(q, scratch) / (float)width;
+  return make_float2(mean, 1.f / sqrtf(var + eps));
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+layer_norm_stream_kernel(const float* stream, const void* y, int y_f32, const void* __restrict__ wy,
+                         const void* __restrict__ by, const void* __restrict__ sy, int wy_f32, float eps_y,
+                         float* stream_out, const void* __restrict__ w, const void* __restrict__ b, int w_f32, float eps,
+                         TO* out, int width) {
+  extern __shared__ float row[];          // [width]
+  __shared__ float scratch[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t base = (int64_t)blockIdx.x * width;
+  if (y != nullptr) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = load_flex(y, y_f32, base + i);
+    __syncthreads();
+    if (wy != nullptr) {
+      const float2 mi = mean_inv(row, width, eps_y, scratch);
+      for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float t = (row[i] - mi.x) * mi.y * load_flex(wy, wy_f32, i);
+        if (by != nullptr) t += load_flex(by, wy_f32, i);
+        if (sy != nullptr) t *= load_flex(sy, wy_f32, i);
+        row[i] = t;
+      }
+    }
+    if (stream != nullptr)
+      for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = stream[base + i] + row[i];
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = stream[base + i];
+  }
+  if (stream_out != nullptr)
+    for (int i = threadIdx.x; i < width; i += blockDim.x) stream_out[base + i] = row[i];
+  if (out == nullptr) return;
+  __syncthreads();
+  const float2 mi = mean_inv(row, width, eps, scratch);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = (row[i] - mi.x) * mi.y * load_flex(w, w_f32, i);
+    if (b != nullptr) v += load_flex(b, w_f32, i);
+    out[base + i] = from_f32<TO>(v);
+  }
+}
+
+constexpr int MAX_WIDTH = 49152;         // floats of shared memory a row may take (192 KiB)
+
+}  // namespace
+
+// stream: float32 [rows, width] or null; y: [rows, width] float32 or bfloat16, or null;
+// wy / by / sy: the norm and the scale of y ([width], one type; wy null: y is added as it is;
+// by, sy may be null); w / b: the norm of the sum (b may be null); out null: only stream_out.
+VOSTI_API int vosti_layer_norm_stream(const float* stream, const void* y, int y_f32, const void* wy, const void* by,
+                                      const void* sy, int wy_f32, float eps_y, float* stream_out, const void* w,
+                                      const void* b, int w_f32, float eps, void* out, int out_f32, int rows, int width,
+                                      cudaStream_t stream_id) {
+  VOSTI_REQUIRE(rows >= 0 && width > 0 && width <= MAX_WIDTH, "layer_norm_stream: bad sizes rows=%d width=%d (at most %d)",
+                rows, width, MAX_WIDTH);
+  VOSTI_REQUIRE(stream != nullptr || y != nullptr, "layer_norm_stream: nothing to norm");
+  VOSTI_REQUIRE(out != nullptr || stream_out != nullptr, "layer_norm_stream: nowhere to write");
+  VOSTI_REQUIRE(out == nullptr || w != nullptr, "layer_norm_stream: a normed result needs a weight");
+  if (rows == 0) return VOSTI_OK;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(layer_norm_stream_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_WIDTH * 4);
+    cudaFuncSetAttribute(layer_norm_stream_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_WIDTH * 4);
+    configured = true;
+  }
+  const size_t smem = (size_t)width * sizeof(float);
+  if (out_f32)
+    vosti_launch(layer_norm_stream_kernel<float>, dim3(rows), dim3(256), smem, stream_id, stream, y, y_f32, wy, by, sy, wy_f32,
+                 eps_y, stream_out, w, b, w_f32, eps, (float*)out, width);
+  else
+    vosti_launch(layer_norm_stream_kernel<bf16>, dim3(rows), dim3(256), smem, stream_id, stream, y, y_f32, wy, by, sy, wy_f32,
+                 eps_y, stream_out, w, b, w_f32, eps, (bf16*)out, width);
+  VOSTI_LAUNCH_CHECK();
+}

@@ -198,6 +198,10 @@ class DecoderModel:
     def logits(self, ctx, hidden: torch.Tensor, residual: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] of the rows (flat token indices) asked for:
         only those rows are gathered, added, normed and multiplied with the head."""
+        if isinstance(hidden, ops.DeferredNormed):
+            # a sublayer output still to be normed, scaled and added: only the wanted rows are
+            hidden = hidden.rows(rows, ctx.status)
+            return self.head.forward(ctx, self.final_norm.forward_add(ctx, hidden, ops.gather_rows(residual, rows, ctx.status))[0])
         if isinstance(hidden, ops.DeferredSum):
             # a float32 stream with sublayer outputs still to be added: add, then gather
             hidden, residual = ops.stream_sum(residual, hidden), None

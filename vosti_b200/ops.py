@@ -799,12 +799,15 @@ def token_gate(z: torch.Tensor, ids: torch.Tensor, side: torch.Tensor, offset: i
 def qkv_store(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], *, nq: int, nkv: int,
               dk: int, dv: int, page_size: int, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
               temp_coef: float, temp_every: int, status: torch.Tensor,
-              freq: Optional[torch.Tensor] = None) -> torch.Tensor:
+              freq: Optional[torch.Tensor] = None, magnitude: float = 1.0,
+              v_first: Optional[torch.Tensor] = None, v_mix: float = 0.0) -> torch.Tensor:
     """After a q | k | v projection: the queries times their temperature
     (1 + coef * ln(floor((p + 1) / every) + 1), 1 if coef is 0) are returned [tokens, nq * dk];
     keys and values go to their cache slots (caches of different widths). With `freq` (float32
     [n]) the first 2n elements of every query and key head are first turned in pairs (i, i + n) by
-    the angle position * freq[i]."""
+    the angle position * freq[i], cos and sin multiplied by `magnitude`. With `v_first` (the values
+    [tokens, nkv * dv] another layer made of the same tokens; rows may be strided) the values
+    stored are (1 - v_mix) * v + v_mix * v_first, formed in float32 and rounded once."""
     qkv = materialize(qkv)
     _contig(qkv, k_cache, v_cache, positions, slot_mapping, freq)
     flag = _same_dtype(qkv, k_cache, v_cache)
@@ -813,12 +816,17 @@ def qkv_store(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optio
         raise KernelError("qkv_store: rotation frequencies are float32")
     if qkv.shape[1] != nq * dk + nkv * (dk + dv):
         raise KernelError("qkv_store: input width does not match the head counts")
+    if v_first is not None and (v_first.dtype != qkv.dtype or tuple(v_first.shape) != (tokens, nkv * dv)
+                                or v_first.stride(1) != 1):
+        raise KernelError("qkv_store: the values to mix in are [tokens, nkv * dv] of the projection's type")
     q = torch.empty((tokens, nq * dk), dtype=qkv.dtype, device=qkv.device)
     num_slots = 0 if k_cache is None else k_cache.numel() // (nkv * dk)
     _check(library().vosti_qkv_store(_p(qkv), _p(q), _p(k_cache), _p(v_cache), _p(positions), _p(slot_mapping),
                                      ctypes.c_int64(num_slots), page_size, tokens, nq, nkv, dk, dv,
                                      ctypes.c_float(temp_coef), int(temp_every), flag, _p(status), _p(freq),
-                                     0 if freq is None else freq.shape[0], _stream()), "qkv_store")
+                                     0 if freq is None else freq.shape[0], ctypes.c_float(magnitude), _p(v_first),
+                                     ctypes.c_int64(0 if v_first is None else v_first.stride(0)), ctypes.c_float(v_mix),
+                                     _stream()), "qkv_store")
     return q
 
 
@@ -890,6 +898,160 @@ def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
             nq, nkv, dk, lists["max_long_q_len"], tokens, ctypes.c_float(scale), window, _p(bias), bias_last, _p(sink),
             _p(ctx.status), _stream()), "attention_prefill_tc_biased")
     return out
+
+
+# ---------------------------------------------------------------- layer norm over the stream
+class DeferredNormed:
+    """A sublayer's output [rows, width] that is still to be layer-normed (weight, optional bias),
+    multiplied element by element by an optional `scale` vector and added to the float32 residual
+    stream: the kernel that next reads the stream (`layer_norm_stream`) does all of it."""
+
+    def __init__(self, y, weight: torch.Tensor, bias: Optional[torch.Tensor], scale: Optional[torch.Tensor], eps: float):
+        self.y = materialize(y)
+        self.weight, self.bias, self.scale, self.eps = weight, bias, scale, float(eps)
+        small = [t for t in (weight, bias, scale) if t is not None]
+        if len({t.dtype for t in small}) > 1:
+            self.weight, self.bias, self.scale = (None if t is None else t.float() for t in (weight, bias, scale))
+        self.shape = tuple(self.y.shape)
+
+    def rows(self, index: torch.Tensor, status: torch.Tensor) -> "DeferredNormed":
+        """The same for the rows `index` names."""
+        return DeferredNormed(gather_rows(self.y, index, status), self.weight, self.bias, self.scale, self.eps)
+
+
+def layer_norm_stream(x, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], eps: float,
+                      out_dtype: Optional[torch.dtype], *, stream: Optional[torch.Tensor] = None,
+                      stream_out: Optional[torch.Tensor] = None):
+    """Layer norm of s = stream + x over a float32 residual stream: (s - mean) / sqrt(var + eps) *
+    weight + bias in float32 (var: the mean of the squared deviations), rounded to `out_dtype`; s
+    goes to `stream_out` (float32, may be `stream`). x is a tensor, None, or a `DeferredNormed`,
+    which is normed and scaled on the way in. Without `out_dtype` only the sum is stored."""
+    y = wy = by = sy = None
+    eps_y = 0.0
+    if isinstance(x, DeferredNormed):
+        y, wy, by, sy, eps_y = x.y, x.weight, x.bias, x.scale, x.eps
+    elif x is not None:
+        y = materialize(x)
+    like = stream if stream is not None else y
+    _contig(stream, stream_out, y, wy, by, sy, weight, bias)
+    if stream is not None and stream.dtype != torch.float32 or stream_out is not None and stream_out.dtype != torch.float32:
+        raise KernelError("layer_norm_stream: the residual stream is float32")
+    if bias is not None and bias.dtype != weight.dtype:
+        raise KernelError("layer_norm_stream: weight and bias must share a dtype")
+    rows, width = like.shape
+    out = None if out_dtype is None else torch.empty((rows, width), dtype=out_dtype, device=like.device)
+    _check(library().vosti_layer_norm_stream(
+        _p(stream), _p(y), 0 if y is None else _is_f32(y), _p(wy), _p(by), _p(sy), 0 if wy is None else _is_f32(wy),
+        ctypes.c_float(eps_y), _p(stream_out), _p(weight), _p(bias), 0 if weight is None else _is_f32(weight),
+        ctypes.c_float(eps), _p(out), 0 if out is None else _is_f32(out), rows, width, _stream()), "layer_norm_stream")
+    return out
+
+
+# ---------------------------------------------------------------- latent attention
+def latent_prep(proj: torch.Tensor, qk: torch.Tensor, c_cache: Optional[torch.Tensor], r_cache: Optional[torch.Tensor],
+                norm_w: torch.Tensor, eps: float, ctx, slot_mapping: Optional[torch.Tensor], *, heads: int, dim: int, rot: int,
+                rank: int, freq: Optional[torch.Tensor], magnitude: float) -> torch.Tensor:
+    """After the q | down | gate projection (csrc/attention_latent.cu): the rotated part of every
+    query head goes to the last `rot` columns of qk [tokens, heads, rank + rot]; the latent
+    (root-mean-square normed with `norm_w`) and the rotated shared key part go to their cache
+    slots; returns sigmoid(gate) float32 [tokens, heads]."""
+    proj = materialize(proj)
+    _contig(proj, qk, c_cache, r_cache, norm_w, slot_mapping, freq)
+    flag = _same_dtype(proj, qk, c_cache, r_cache)
+    tokens = proj.shape[0]
+    if proj.shape[1] != heads * (dim + rot) + rank + rot + heads or tuple(qk.shape) != (tokens, heads, rank + rot):
+        raise KernelError("latent_prep: widths do not match the head sizes")
+    gate = torch.empty((tokens, heads), dtype=torch.float32, device=proj.device)
+    num_slots = 0 if c_cache is None else c_cache.numel() // rank
+    _check(library().vosti_latent_prep(_p(proj), _p(qk), _p(gate), _p(c_cache), _p(r_cache), _p(norm_w), _is_f32(norm_w),
+                                       ctypes.c_float(eps), _p(ctx.positions), _p(slot_mapping), ctypes.c_int64(num_slots),
+                                       tokens, heads, dim, rot, rank, _p(freq), ctypes.c_float(magnitude), flag,
+                                       _p(ctx.status), _stream()), "latent_prep")
+    return gate
+
+
+def head_project(x: torch.Tensor, m: torch.Tensor, y: torch.Tensor, *, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[t, h, :] = gate[t, h] * (x[t, h, :] @ m[h]) on the CUDA cores, float32 arithmetic. x [tokens,
+    heads, in], m [heads, in, out] and y [tokens, heads, out] may be strided views (unit stride
+    along x's and y's last axis); gate float32 [tokens, heads]."""
+    tokens, heads, inner = x.shape
+    if tuple(m.shape[:2]) != (heads, inner) or tuple(y.shape) != (tokens, heads, m.shape[2]):
+        raise KernelError("head_project: shapes do not fit")
+    if tokens and (x.stride(2) != 1 or y.stride(2) != 1):
+        raise KernelError("head_project: the last axis of x and y must be contiguous")
+    _contig(gate)
+    _check(library().vosti_head_project(
+        _p(x), _is_f32(x), ctypes.c_int64(x.stride(0)), ctypes.c_int64(x.stride(1)), _p(m), _is_f32(m),
+        ctypes.c_int64(m.stride(0)), ctypes.c_int64(m.stride(1)), ctypes.c_int64(m.stride(2)), _p(gate), _p(y), _is_f32(y),
+        ctypes.c_int64(y.stride(0)), ctypes.c_int64(y.stride(1)), tokens, heads, inner, m.shape[2], _stream()), "head_project")
+    return y
+
+
+LATENT_SEGMENT = 256           # keys per segment when few query rows share the GPU
+LATENT_SPLIT_MAX_ROWS = 2048   # (token, head) rows up to which the keys are cut into segments
+
+
+def latent_attend(ctx, qk: torch.Tensor, c_cache: torch.Tensor, r_cache: torch.Tensor, group, *, scale: float,
+                  window: int = 0) -> torch.Tensor:
+    """Causal softmax attention of every (token, head) row of qk [tokens, heads, rank + rot] over the
+    cached latents [pages, 1, page_size, rank] and shared rotated key parts [.., rot] of its
+    request; returns the weighted latents, float32 [tokens, heads, rank]."""
+    _contig(qk, c_cache, r_cache)
+    flag = _same_dtype(qk, c_cache, r_cache)
+    tokens, heads = qk.shape[0], qk.shape[1]
+    rank, rot = c_cache.shape[-1], r_cache.shape[-1]
+    out = torch.empty((tokens, heads, rank), dtype=torch.float32, device=qk.device)
+    num_pages = c_cache.shape[0]
+    segments, scratch = 1, None
+    if tokens * heads <= LATENT_SPLIT_MAX_ROWS and ctx.max_kv_len > LATENT_SEGMENT:
+        segments = -(-ctx.max_kv_len // LATENT_SEGMENT)
+        scratch = _workspace(qk.device, tokens * heads * segments * (rank + 2))
+    _check(library().vosti_latent_attend(
+        _p(qk), _p(c_cache), _p(r_cache), _p(out), _p(ctx.positions), _p(ctx.request_of), _p(group.block_table),
+        group.block_table.shape[1], group.page_size, num_pages, None, tokens, heads, rank, rot, ctypes.c_float(scale),
+        window, _p(scratch), LATENT_SEGMENT, segments, flag, _p(ctx.status), _stream()), "latent_attend",
+        kernels=2 if segments > 1 else 1)
+    return out
+
+
+# ---------------------------------------------------------------- selective scan
+def scan_conv(xz: torch.Tensor, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], state: torch.Tensor, tail_offset: int,
+              ctx, *, inner: int, taps: int) -> torch.Tensor:
+    """silu(causal convolution) of the first `inner` columns of xz [tokens, >= inner] per channel
+    (csrc/selective_scan.cu); the inputs before a portion come from the tail [taps - 1, inner] kept
+    `tail_offset` floats into the request's state slot, which is then moved on."""
+    xz = materialize(xz)
+    _contig(xz, conv_w, conv_b, state)
+    if conv_b is not None and conv_b.dtype != conv_w.dtype or state.dtype != torch.float32:
+        raise KernelError("scan_conv: the convolution's tensors share a type and the state is float32")
+    tokens = xz.shape[0]
+    out = torch.empty((tokens, inner), dtype=xz.dtype, device=xz.device)
+    _check(library().vosti_scan_conv(
+        _p(xz), ctypes.c_int64(xz.shape[1]), _p(conv_w), _p(conv_b), _is_f32(conv_w), _p(state), ctypes.c_int64(state.shape[1]),
+        ctypes.c_int64(tail_offset), _p(ctx.request_of), _p(ctx.cu_q), _p(ctx.state_slots), state.shape[0], ctx.num_requests,
+        tokens, inner, taps, _p(out), _is_f32(xz), _p(ctx.status), _stream()), "scan_conv", kernels=2 if taps > 1 else 1)
+    return out
+
+
+def scan_run(x: torch.Tensor, dtp: torch.Tensor, dt_bias: Optional[torch.Tensor], bc: torch.Tensor, a_log: torch.Tensor,
+             d_skip: Optional[torch.Tensor], xz: torch.Tensor, state: torch.Tensor, ctx, *, inner: int, states: int) -> torch.Tensor:
+    """The selective-scan recurrence over every request's tokens of this step, from and to its state
+    slot: x [tokens, inner] (convolved), dtp float32 [tokens, inner] (step sizes before bias and
+    softplus), bc float32 [tokens, 2 * states], z = the columns [inner, 2 * inner) of xz. Returns
+    (S C + D x) * silu(z) in x's type."""
+    _contig(x, dtp, dt_bias, bc, a_log, d_skip, xz, state)
+    small = [t for t in (dt_bias, a_log, d_skip) if t is not None]
+    if len({t.dtype for t in small}) > 1 or dtp.dtype != torch.float32 or bc.dtype != torch.float32 or state.dtype != torch.float32:
+        raise KernelError("scan_run: the small tensors share a type; step sizes, B | C and the state are float32")
+    if xz.dtype != x.dtype or xz.shape[1] < 2 * inner or tuple(bc.shape) != (x.shape[0], 2 * states):
+        raise KernelError("scan_run: shapes do not fit")
+    y = torch.empty_like(x)
+    z = xz[:, inner:]
+    _check(library().vosti_scan_run(
+        _p(x), _p(dtp), _p(dt_bias), _p(bc), _p(a_log), _p(d_skip), _is_f32(a_log), _p(z), ctypes.c_int64(xz.shape[1]),
+        _p(state), ctypes.c_int64(state.shape[1]), _p(ctx.cu_q), _p(ctx.state_slots), state.shape[0], ctx.num_requests,
+        inner, states, _p(y), _is_f32(x), _p(ctx.status), _stream()), "scan_run")
+    return y
 
 
 # ---------------------------------------------------------------- gated delta rule

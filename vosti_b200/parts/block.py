@@ -217,3 +217,80 @@ class StreamPreNormBlock:
 
 
 register_part("arrangement", "pre_norm_stream", StreamPreNormBlock, replace=True)
+
+
+class SandwichStreamBlock(StreamPreNormBlock):
+    """'sandwich_stream': norms before and after every sublayer over a float32 residual stream, and
+    an optional learned scale on what joins the stream,
+
+        x <- x + s1 * out_norm1(mixer(norm1(x)));   x <- x + s2 * out_norm2(ff(norm2(x)))
+
+    `LayerSpec.norm` names the norms before the sublayers, `LayerSpec.out_norm` those after them (a
+    norm with `defer`, such as `LayerNormStream`); with `LayerSpec.layer_scale` the vectors s1, s2
+    exist. Adds are deferred like the other blocks': a sublayer's output travels as an
+    `ops.DeferredNormed` and the kernel of the next norm that reads the stream norms it, scales
+    it, adds it and norms the sum, one launch per sublayer boundary.
+
+    Checkpoint names: `LayerSpec.names` maps the roles "input_norm", "mixer_out_norm", "post_norm",
+    "ff_out_norm", "mixer", "feed_forward", "mixer_scale", "ff_scale" to name fragments; a norm's
+    `weight` tensor and a scale are called by the fragment itself, every other tensor
+    `<fragment>.<key>`. A layer without a feed-forward has neither its norms nor its scale; a
+    checkpoint may carry them all the same."""
+
+    def __init__(self, spec: LayerSpec, hidden_size: int):
+        super().__init__(spec, hidden_size)
+        if spec.out_norm is None or spec.token_input is not None:
+            raise ConfigError("sandwich_stream block: it needs an out_norm and takes no token input")
+        self.mixer_out_norm = build_norm(spec.out_norm, hidden_size)
+        self.ff_out_norm = build_norm(spec.out_norm, hidden_size)          # built also without a feed-forward: its tensors may be present
+        if self.post_norm is None:
+            self.unused_post_norm = build_norm(spec.norm, hidden_size)
+        if not hasattr(self.mixer_out_norm, "defer"):
+            raise ConfigError("sandwich_stream block: the out_norm must be one that can be deferred into the stream's kernel")
+        self.scaled = bool(spec.layer_scale)
+        self.mixer_scale = self.ff_scale = None
+
+    def _children(self):
+        n = self.spec.name_of
+        yield n("input_norm"), self.input_norm
+        yield n("mixer"), self.mixer
+        yield n("mixer_out_norm"), self.mixer_out_norm
+        if self.feed_forward is not None:
+            yield n("post_norm"), self.post_norm
+            yield n("feed_forward"), self.feed_forward
+            yield n("ff_out_norm"), self.ff_out_norm
+
+    def _scales(self):
+        n = self.spec.name_of
+        if self.scaled:
+            yield n("mixer_scale"), "mixer_scale", False
+            yield n("ff_scale"), "ff_scale", self.feed_forward is None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        import dataclasses
+        specs = super().weight_specs()
+        for name, _, unused in self._scales():
+            specs[name] = WeightSpec((self.mixer.hidden_size,), init="norm", std=0.1, optional=unused)
+        if self.feed_forward is None:
+            # tensors of the absent sublayer: taken if the checkpoint has them, never read
+            n = self.spec.name_of
+            for fragment, part in ((n("post_norm"), self.unused_post_norm), (n("ff_out_norm"), self.ff_out_norm)):
+                for key, w in part.weight_specs().items():
+                    specs[fragment if key == "weight" else f"{fragment}.{key}"] = dataclasses.replace(w, optional=True)
+        return specs
+
+    def load(self, tensors, dtype):
+        super().load(tensors, dtype)
+        for name, attribute, unused in self._scales():
+            setattr(self, attribute, None if unused else tensors[name])
+
+    def forward(self, ctx, hidden, residual, cache, writes_cache=True):
+        normed, residual = self.input_norm.forward_add(ctx, hidden, residual)
+        out = self.mixer_out_norm.defer(self.mixer.forward(ctx, normed, cache, writes_cache), self.mixer_scale)
+        if self.feed_forward is not None:
+            normed, residual = self.post_norm.forward_add(ctx, out, residual)
+            out = self.ff_out_norm.defer(self.feed_forward.forward(ctx, normed), self.ff_scale)
+        return out, residual
+
+
+register_part("arrangement", "sandwich_stream", SandwichStreamBlock, replace=True)

@@ -123,3 +123,57 @@ class StreamRMSNorm(Norm):
 
 
 register_part("norm", "rms_stream", StreamRMSNorm, replace=True)
+
+
+class LayerNormStream(Norm):
+    """Layer norm with weight and bias for models whose residual stream is float32 in both serving
+    types: (x - mean) / sqrt(var + eps) * weight + bias with var the mean of the squared
+    deviations, in float32, rounded to the serving type. Parameters: `eps`; `bias` (default true);
+    `bias_name`, what the checkpoint calls the bias beside the weight (default "bias");
+    `out_dtype` "float32" keeps the normed rows unrounded. `forward_add` takes the stream and what
+    is still to be added to it: a tensor, or an `ops.DeferredNormed` (a sublayer output that is
+    itself normed and scaled on its way into the stream); the sum is stored as the new stream."""
+
+    def __init__(self, spec: PartSpec, width: int):
+        super().__init__(spec, width)
+        self.eps = float(spec["eps"])
+        self.has_bias = bool(spec.get("bias", True))
+        self.bias_key = str(spec.get("bias_name", "bias"))
+        self.float32_out = spec.get("out_dtype") == "float32"
+        self.width = width
+        self.weight = self.bias = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs = {"weight": WeightSpec((self.width,), init="norm", std=0.1)}
+        if self.has_bias:
+            specs[self.bias_key] = WeightSpec((self.width,), std=0.1)
+        return specs
+
+    def load(self, tensors, dtype):
+        self.weight, self.bias = tensors["weight"], tensors.get(self.bias_key)
+        if self.bias is not None and self.bias.dtype != self.weight.dtype:
+            self.weight, self.bias = self.weight.float(), self.bias.float()
+
+    def _out(self, ctx):
+        return torch.float32 if self.float32_out else ctx.dtype
+
+    def forward(self, ctx, x):
+        if x.dtype == torch.float32:
+            return ops.layer_norm_stream(None, self.weight, self.bias, self.eps, self._out(ctx), stream=x)
+        return ops.layer_norm_stream(x, self.weight, self.bias, self.eps, self._out(ctx))
+
+    def forward_add(self, ctx, x, residual):
+        if residual is None:
+            first = x.y if isinstance(x, ops.DeferredNormed) else ops.materialize(x)
+            residual = torch.empty(first.shape, dtype=torch.float32, device=first.device)
+            return ops.layer_norm_stream(x, self.weight, self.bias, self.eps, self._out(ctx), stream_out=residual), residual
+        return ops.layer_norm_stream(x, self.weight, self.bias, self.eps, self._out(ctx), stream=residual,
+                                     stream_out=residual), residual
+
+    def defer(self, y, scale):
+        """`y` as something this norm (and the `scale` vector, if any) is still to be applied to, for
+        the kernel that adds it to the stream."""
+        return ops.DeferredNormed(y, self.weight, self.bias, scale, self.eps)
+
+
+register_part("norm", "layer_norm_stream", LayerNormStream, replace=True)

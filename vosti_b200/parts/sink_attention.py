@@ -14,7 +14,12 @@ of them optional and a parameter of the spec:
   by distance n = i - j: row n below rows // 2, then logarithmic steps,
   min(rows - 1, half + floor(ln(n / half) / ln(far / half) * (rows - half))), which reach the
   last row at distance `far`. The scale does not multiply the bias;
-* `sink`: a learned logit per head joins the softmax denominator once, with no key or value.
+* `sink`: a learned logit per head joins the softmax denominator once, with no key or value;
+* `value_mix`: "source" publishes this layer's values of the step's tokens for later layers;
+  "mix" replaces its own values by (1 - l) v + l v_source before they are cached, with the learned
+  scalar l = `vmix` and v_source the values the source layer made of the same tokens (the source
+  runs earlier in the same step; both have the same kv heads and value width). A source layer's
+  checkpoint may carry an unused `vmix`.
 
 Other parameters: num_heads, num_kv_heads (query head h reads kv head h // (heads / kv_heads)),
 head_dim, v_head_dim, scale, window (0: every earlier key). Keys and values live in the paged
@@ -59,8 +64,12 @@ class SinkAttention(Mixer):
         self.has_sink = bool(spec.get("sink", False))
         self.sink_value = spec.get("sink_value")
         self.chunk = int(spec.get("chunk", 0) or 0)
+        self.value_mix = spec.get("value_mix")
+        if self.value_mix not in (None, "source", "mix"):
+            raise ConfigError("sink_attention: value_mix is 'source' or 'mix'")
+        self.mix = 0.0
         self.rotation = build_position(spec.get("position"), hidden_size, self.dk)
-        self.freq = None
+        self.freq, self.magnitude = None, 1.0
         if self.has_sink and self.sink_value is not None:
             raise ConfigError("sink_attention: a learned sink or a constant one, not both")
         if self.chunk < 0 or (self.chunk and self.window):
@@ -85,6 +94,8 @@ class SinkAttention(Mixer):
             specs["rel"] = WeightSpec((self.bias_rows, nq), std=1.0)
         if self.has_sink:
             specs["sink"] = WeightSpec((nq,), std=1.0)
+        if self.value_mix is not None:
+            specs["vmix"] = WeightSpec((), std=0.3, optional=self.value_mix == "source")
         return specs
 
     def load(self, tensors, dtype):
@@ -93,6 +104,8 @@ class SinkAttention(Mixer):
         self.w_qkv = prepare_weight(torch.cat([p.to(common) for p in parts], dim=0).contiguous(), dtype)
         self.w_o = prepare_weight(tensors["o"], dtype)
         self.sink = tensors["sink"].float().contiguous() if self.has_sink else None
+        if self.value_mix == "mix":
+            self.mix = float(tensors["vmix"].float().item())
         if self.bias_rows:
             # by distance, up to the first one that reaches the table's last row: [heads, distances],
             # in base-2 units because the kernels' softmax runs in base 2
@@ -108,6 +121,7 @@ class SinkAttention(Mixer):
     def setup(self, device, dtype):
         if self.rotation is not None:
             self.freq = self.rotation.frequencies().to(device=device, dtype=torch.float32).contiguous()
+            self.magnitude = float(self.rotation.magnitude()) if hasattr(self.rotation, "magnitude") else 1.0
         if self.sink_value is not None:
             self.sink = torch.full((self.nq,), float(self.sink_value), dtype=torch.float32, device=device)
 
@@ -119,11 +133,18 @@ class SinkAttention(Mixer):
 
     def forward(self, ctx, x, cache, writes_cache: bool = True):
         group = ctx.group(cache.group)
-        qkv = linear(ctx, x, self.w_qkv)
+        qkv = ops.materialize(linear(ctx, x, self.w_qkv))
+        v_source = None
+        if self.value_mix == "source":
+            ctx.extras["value_mix.source"] = qkv[:, self.nq * self.dk + self.nkv * self.dk:]
+        elif self.value_mix == "mix":
+            v_source = ctx.extras.get("value_mix.source")
+            if v_source is None:
+                raise ConfigError("sink_attention: a layer mixes values in, but no source layer ran before it in this step")
         q = ops.qkv_store(qkv, cache.k if writes_cache else None, cache.v if writes_cache else None, nq=self.nq,
                           nkv=self.nkv, dk=self.dk, dv=self.dv, page_size=group.page_size, positions=ctx.positions,
                           slot_mapping=group.slot_mapping, temp_coef=self.temp_coef, temp_every=self.temp_every,
-                          status=ctx.status, freq=self.freq)
+                          status=ctx.status, freq=self.freq, magnitude=self.magnitude, v_first=v_source, v_mix=self.mix)
         attn = ops.attention_sink(ctx, q, cache.k, cache.v, group, nq=self.nq, nkv=self.nkv, dk=self.dk, dv=self.dv,
                                   scale=self.scale, window=self.window, bias=self.bias_table, sink=self.sink, chunk=self.chunk)
         return linear(ctx, attn, self.w_o, out_dtype=torch.float32)
