@@ -33,6 +33,11 @@ and decode steps at batch 8 and 1 for each, with their shares of the measured pe
 gated-delta layers alternating with layers of chunked rotary attention beside a generalized
 delta rule, an expert feed-forward in every layer) beside Mugizen, the engine's closest
 model, at the same sizes.
+
+`--design beralix` does the same for the Beralix design (layers normed before and after every
+sublayer over a float32 stream: latent attention, windowed attention with value mixing and a
+selective scan in turn, dense feed-forwards) beside Mugizen with dense feed-forwards at the
+same sizes (`--design-sizes s,m`).
 """
 from __future__ import annotations
 
@@ -408,10 +413,48 @@ def vivesun_flops(size, tokens):
     return 2.0 * tokens * per_token + 2.0 * V * W + scores + state
 
 
+def beralix_config(size):
+    """A Beralix config.json of these sizes: latent attention (a latent of 512, 64 rotated and 128
+    unrotated elements a head), windowed attention (window 1,024, whole-head rescaled rotation),
+    a selective scan (twice the width, 16 states, 4 taps) and windowed attention again; the two
+    windowed layers mix values. Every layer has a dense feed-forward."""
+    H, G, W = size["heads"], size["kv"], size["width"]
+    yarn = dict(factor=8.0, original=4096, fast=32.0, slow=1.0)
+    mlp = dict(kind="dense", ff=size["ff"])
+    latent = dict(type="latent_attention", mlp=mlp, mixer=dict(heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=512, scale=192 ** -0.5,
+                                                               rot=dict(base=10000.0, dims=64, scaling=yarn)))
+    window = dict(type="attention", mlp=mlp, mixer=dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=1024),
+                                                        v_mix=True, rot=dict(base=500000.0, dims=128, scaling=yarn)))
+    scan = dict(type="mamba1", mlp=mlp, mixer=dict(inner=2 * W, state=16, conv=4, dt_rank=W // 16))
+    order = [latent, window, scan, window]
+    return dict(architecture="Beralix", vocab=size["vocab"], width=W, norm=dict(eps=1e-5), logit_softcap=30.0,
+                layers=[order[i % 4] for i in range(size["layers"])])
+
+
+def beralix_flops(size, tokens):
+    """Multiply-add work of one prompt, times two, for `beralix_config(size)`, as the engine computes
+    it: the latent attention scores and sums over the cached latents (rank + rotated elements a key
+    for the score, rank for the sum), after carrying the query into the latent space."""
+    W, H, G, F, L, V, d = size["width"], size["heads"], size["kv"], size["ff"], size["layers"], size["vocab"], 128
+    rank, rot, inner, N, low = 512, 64, 2 * W, 16, W // 16
+    latent = W * (H * (d + rot) + rank + rot + H) + 2 * H * d * rank + H * d * W
+    window = W * (H + 2 * G) * d + H * d * W
+    scan = W * 2 * inner + inner * (low + 2 * N) + low * inner + inner * W + 3 * inner * N
+    kinds = [latent, window, scan, window]
+    per_token = sum(kinds[i % 4] + 3 * W * F for i in range(L))
+    pairs_all = tokens * (tokens + 1) / 2
+    pairs_window = sum(min(t + 1, 1024) for t in range(tokens))
+    scores = sum((H * (2 * rank + rot) * 2.0 * pairs_all) if i % 4 == 0 else (H * d * 4.0 * pairs_window) if i % 4 in (1, 3) else 0.0
+                 for i in range(L))
+    return 2.0 * tokens * per_token + 2.0 * V * W + scores
+
+
 def design_flops(size, tokens, design):
     """Multiply-add work of one prompt of `tokens` tokens, times two: the products and the attention."""
     if design == "vivesun":
         return vivesun_flops(size, tokens)
+    if design == "beralix":
+        return beralix_flops(size, tokens)
     W, H, G, F, L, V = size["width"], size["heads"], size["kv"], size["ff"], size["layers"], size["vocab"]
     d = 128
     attention = W * (H + 2 * G) * d + H * d * W
@@ -439,6 +482,8 @@ def design_engine(kind, size, max_batch):
     elif kind == "vivesun":
         config, shapes = vivesun_config(size)
         spec = model_spec_from_config(config, shapes)
+    elif kind == "beralix":
+        spec = model_spec_from_config(beralix_config(size))
     else:
         spec = model_spec_from_config(qwen3(size["layers"], size["width"], size["heads"], size["kv"], size["ff"],
                                             context=CONTEXT + 2048) | {"vocab_size": size["vocab"]})
@@ -483,9 +528,12 @@ def design_one(args, name, kind) -> dict:
     return entry
 
 
+BESIDE = {"mugizen": "qwen3", "vivesun": "mugizen", "beralix": "mugizen"}      # the engine's closest other model
+
+
 def design_main(args) -> int:
     """Prefill and decode of a design beside the engine's closest other model (Mugizen beside Qwen3,
-    Vivesun beside Mugizen) at equal sizes; one JSON line. Every
+    Vivesun and Beralix beside Mugizen) at equal sizes; one JSON line. Every
     model is measured in a process of its own (this program started again with --design-one), so
     that no model's scratch buffers, graphs or allocator state reach the next one's timings."""
     if args.design_one:
@@ -496,8 +544,10 @@ def design_main(args) -> int:
     out = {}
     for name in args.design_sizes.split(","):
         size = DESIGN_SIZES[name]
+        if args.design == "beralix" and size["moe"]:
+            continue                          # the design's feed-forwards are dense
         row = {}
-        for kind in (args.design, "mugizen" if args.design == "vivesun" else "qwen3"):
+        for kind in (args.design, BESIDE[args.design]):
             if kind == "qwen3" and size["moe"]:
                 continue                      # the engine has no other model with experts to stand beside
             child = subprocess.run([sys.executable, os.path.abspath(__file__), "--design", args.design, "--design-one",
@@ -509,7 +559,7 @@ def design_main(args) -> int:
                 raise RuntimeError(f"measuring {kind} at size {name} failed (exit code {child.returncode})")
             row[kind] = json.loads(lines[-1])
         out[name] = {"sizes": {k: v for k, v in size.items()}, **row}
-    print(json.dumps({"design": args.design, "beside": ("mugizen" if args.design == "vivesun" else "qwen3") + " at equal sizes", "context": CONTEXT, "page_size": PAGE,
+    print(json.dumps({"design": args.design, "beside": BESIDE[args.design] + " at equal sizes", "context": CONTEXT, "page_size": PAGE,
                       "steps": args.steps, "warmup": args.warmup, "dtype": "bf16", "peaks": peak_kind,
                       "data": "synthetic: random token ids, random-init weights", "results": out}))
     return 0
@@ -537,8 +587,8 @@ def main() -> int:
                         help="read every step's tokens before the next step is planned (default: the engine's async scheduling)")
     parser.add_argument("--batch-invariant", default="off", choices=["off", "decode", "full"],
                         help="measure with the engine's bitwise-invariance modes (the default run has them off)")
-    parser.add_argument("--design", default="", choices=["", "mugizen", "vivesun"],
-                        help="measure this design beside Qwen3 at equal layer sizes instead of the headline")
+    parser.add_argument("--design", default="", choices=["", "mugizen", "vivesun", "beralix"],
+                        help="measure this design beside the engine's closest other model at equal layer sizes instead of the headline")
     parser.add_argument("--design-sizes", default="s,m,moe", help="which of the sizes s, m, moe (comma-separated)")
     parser.add_argument("--design-one", default="", help=argparse.SUPPRESS)      # size:design, one model in this process
     args = parser.parse_args()

@@ -299,7 +299,9 @@ def latent_spec(block, eps, gate=True):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,dim,rot,dv,rank,scaling,page", [
     (3, 20, 6, 10, 40, YARN, 8), (1, 8, 2, 8, 8, None, 4), (5, 12, 10, 24, 24, None, 8), (4, 32, 16, 48, 64, YARN, 16),
-    (2, 7, 4, 5, 33, YARN, 4), (2, 64, 32, 64, 160, None, 16), (1, 16, 8, 16, 300, YARN, 8)])
+    (2, 7, 4, 5, 33, YARN, 4), (2, 64, 32, 64, 160, None, 16), (1, 16, 8, 16, 300, YARN, 8),
+    # sizes the tensor-core kernel takes in bfloat16: a tile of 16 rows is one token, four tokens, or cuts across tokens
+    (16, 128, 64, 128, 512, YARN, 16), (4, 32, 32, 48, 128, None, 16), (3, 64, 32, 64, 256, YARN, 8), (40, 16, 64, 16, 128, None, 4)])
 def test_latent_attention_mixer_against_plain(dtype, heads, dim, rot, dv, rank, scaling, page):
     gen = torch.Generator().manual_seed(heads * 100 + rank)
     width, T, eps = 72, 150, 2e-6
@@ -333,15 +335,44 @@ def test_latent_attention_without_a_gate():
     close(run_mixer(mixer, harness, x, (T,), torch.float32), want, torch.float32)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_one_latent_far_back_decides_the_row(dtype):
+def test_latent_attention_of_unequal_requests_in_one_step_on_the_tensor_cores():
+    """A long request decoding one token, a portion in the middle of another and a whole short
+    prompt in one step: every row equals its request alone in the plain form."""
+    gen = torch.Generator().manual_seed(12)
+    width, eps, page, dtype = 96, 1e-5, 16, torch.bfloat16
+    block = latent_block(16, 32, 32, 16, 128, 0.3, 10000.0, YARN)
+    mixer = build_mixer(latent_spec(block, eps), width, None)
+    W = weights_of(mixer, gen)
+    give(mixer, W, dtype)
+    xs = {r: rounded(n, width, gen=gen) for r, n in (("a", 420), ("b", 77), ("c", 3))}
+    want = {r: plain.latent_attention(x.double(), {k: v.double() for k, v in W.items()}, block, eps).float() for r, x in xs.items()}
+    harness = Harness([mixer.cache_spec()], [None], dtype, num_pages=40, page_size=page)
+    cache = harness.cache.layer_caches[0]
+    run = lambda ctx, rows: ops.materialize(mixer.forward(ctx, torch.cat(rows).to(DEV, dtype), cache)).float().cpu()
+    got = {r: [] for r in xs}
+    got["a"].append(run(harness.context([StepEntry("a", [0] * 419)]), [xs["a"][:419]]))
+    got["b"].append(run(harness.context([StepEntry("b", [0] * 20)]), [xs["b"][:20]]))
+    rows = run(harness.context([StepEntry("a", [0]), StepEntry("b", [0] * 37), StepEntry("c", [0] * 3)]),
+               [xs["a"][419:], xs["b"][20:57], xs["c"]])
+    got["a"].append(rows[:1]); got["b"].append(rows[1:38]); got["c"].append(rows[38:])
+    rows = run(harness.context([StepEntry("b", [0] * 20)]), [xs["b"][57:]])
+    got["b"].append(rows)
+    assert int(harness.status.item()) == 0
+    for r in xs:
+        close(torch.cat(got[r]), want[r], dtype, r)
+        worst = (torch.cat(got[r]) - want[r]).abs().max() / want[r].abs().max()
+        assert float(worst) < 0.05, (r, float(worst))
+
+
+@pytest.mark.parametrize("dtype,rank,rot", [(torch.float32, 16, 4), (torch.bfloat16, 16, 4), (torch.bfloat16, 128, 32)])
+def test_one_latent_far_back_decides_the_row(dtype, rank, rot):
     """Causal attention over everything: a key hundreds of tokens back, at the first position, next
     to a page border and next to the borders of the pieces the kernel cuts long contexts into
     must weigh as the plain form says. The projections are rows of the identity, so that the
     mixer's input is the q | down | gate row itself; the first latent element of every token is
     zero but the target's, head 0's unrotated key matrix reads that element alone, and the last
     query looks for it."""
-    heads, dim, rot, dv, rank, page, eps = 2, 8, 4, 8, 16, 16, 1e-6
+    heads, dim, dv, page, eps = 2, 8, 8, 16, 1e-6
     gen = torch.Generator().manual_seed(17)
     qw = heads * (dim + rot)
     width = qw + rank + rot + heads
@@ -359,11 +390,12 @@ def test_one_latent_far_back_decides_the_row(dtype):
     base[:, qw] = 0.0                                     # the first latent element
     base[:, qw + rank + rot:] = rounded(T, heads, gen=gen)
     Wd = {k: v.double() for k, v in W.items()}
-    ctx_cut = ops.LATENT_SEGMENT
+    ctx_cut, small_cut = ops.LATENT_SEGMENT, ops.LATENT_MMA_SEGMENT       # the pieces of either kernel
     assert T > 2 * ctx_cut
-    for target in (0, 1, page - 1, page, ctx_cut - 1, ctx_cut, ctx_cut + 1, 2 * ctx_cut - 1, 2 * ctx_cut, T - 2, T - 1):
+    for target in (0, 1, page - 1, page, 63, 64, small_cut - 1, small_cut, small_cut + 1, ctx_cut - 1, ctx_cut, ctx_cut + 1,
+                   2 * ctx_cut - 1, 2 * ctx_cut, T - 2, T - 1):
         x = base.clone()
-        x[target, qw] = 2.0                               # after the unit-RMS norm about sqrt(rank) * 2 / |row|
+        x[target, qw] = 2.0 * math.sqrt(rank / 16)        # after the unit-RMS norm about 3.7
         x[T - 1, 0] = 16.0                                # head 0's query, first unrotated element
         want = plain.latent_attention(x.double(), Wd, block, eps).float()
         hidden = x.clone()

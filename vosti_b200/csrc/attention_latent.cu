@@ -433,3 +433,20 @@ VOSTI_API int vosti_latent_attend(const void* qk, const void* c_cache, const voi
 #undef VOSTI_LA
   VOSTI_LAUNCH_CHECK();
 }
+
+// The merge alone, for a kernel that left the (m, l, sum) records itself: partial float32
+// [tokens * heads, segments, rank + 2]; out float32 [tokens, heads, rank].
+VOSTI_API int vosti_latent_merge(const float* partial, int segments, float* out, int tokens, int heads, int rank,
+                                 cudaStream_t stream) {
+  VOSTI_REQUIRE(partial != nullptr && segments >= 1 && tokens >= 0 && heads > 0 && rank > 0 && rank <= LATENT_MAX_RANK,
+                "latent_merge: bad sizes");
+  if (tokens == 0) return VOSTI_OK;
+  const int64_t blocks = ((int64_t)tokens * heads + WARPS - 1) / WARPS;
+  VOSTI_REQUIRE(blocks <= 0x7fffffffLL, "latent_merge: too many (token, head) pairs");
+  const dim3 grid((unsigned)blocks), block(WARPS * 32);
+  if (rank <= 128) vosti_launch(latent_merge_kernel<4>, grid, block, 0, stream, partial, segments, out, (const int*)nullptr, tokens, heads, rank);
+  else if (rank <= 256) vosti_launch(latent_merge_kernel<8>, grid, block, 0, stream, partial, segments, out, (const int*)nullptr, tokens, heads, rank);
+  else if (rank <= 512) vosti_launch(latent_merge_kernel<16>, grid, block, 0, stream, partial, segments, out, (const int*)nullptr, tokens, heads, rank);
+  else vosti_launch(latent_merge_kernel<32>, grid, block, 0, stream, partial, segments, out, (const int*)nullptr, tokens, heads, rank);
+  VOSTI_LAUNCH_CHECK();
+}

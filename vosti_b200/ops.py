@@ -989,24 +989,43 @@ def head_project(x: torch.Tensor, m: torch.Tensor, y: torch.Tensor, *, gate: Opt
 
 LATENT_SEGMENT = 256           # keys per segment when few query rows share the GPU
 LATENT_SPLIT_MAX_ROWS = 2048   # (token, head) rows up to which the keys are cut into segments
+LATENT_MMA_SEGMENT = 128       # the same for the tensor-core kernel, whose CTA takes 16 or 32 rows
+LATENT_MMA_SPLIT_BELOW = 296   # CTAs (two per SM) below which it cuts the keys
 
 
 def latent_attend(ctx, qk: torch.Tensor, c_cache: torch.Tensor, r_cache: torch.Tensor, group, *, scale: float,
                   window: int = 0) -> torch.Tensor:
     """Causal softmax attention of every (token, head) row of qk [tokens, heads, rank + rot] over the
     cached latents [pages, 1, page_size, rank] and shared rotated key parts [.., rot] of its
-    request; returns the weighted latents, float32 [tokens, heads, rank]."""
+    request; returns the weighted latents, float32 [tokens, heads, rank]. bfloat16 with a rank of
+    128, 256 or 512 and a rotated part in multiples of 32 runs on the tensor cores
+    (csrc/attention_latent_mma.cu), everything else on the CUDA cores (csrc/attention_latent.cu)."""
     _contig(qk, c_cache, r_cache)
     flag = _same_dtype(qk, c_cache, r_cache)
     tokens, heads = qk.shape[0], qk.shape[1]
     rank, rot = c_cache.shape[-1], r_cache.shape[-1]
     out = torch.empty((tokens, heads, rank), dtype=torch.float32, device=qk.device)
     num_pages = c_cache.shape[0]
+    lib = library()
     segments, scratch = 1, None
+    if not flag and window >= 0 and lib.vosti_latent_attend_mma_fits(rank, rot):
+        rows = ctx.max_q_len * heads
+        ctas = -(-rows // (32 if rows > 16 else 16)) * ctx.num_requests
+        if ctas < LATENT_MMA_SPLIT_BELOW and ctx.max_kv_len > LATENT_MMA_SEGMENT:
+            segments = -(-ctx.max_kv_len // LATENT_MMA_SEGMENT)
+            scratch = _workspace(qk.device, tokens * heads * segments * (rank + 2))
+        _check(lib.vosti_latent_attend_mma(
+            _p(qk), _p(c_cache), _p(r_cache), _p(out), _p(ctx.positions), _p(ctx.cu_q), _p(group.block_table),
+            group.block_table.shape[1], group.page_size, num_pages, ctx.num_requests, ctx.max_q_len, heads, rank, rot,
+            ctypes.c_float(scale), window, _p(scratch), LATENT_MMA_SEGMENT, segments, _p(ctx.status), _stream()),
+            "latent_attend_mma")
+        if segments > 1:
+            _check(lib.vosti_latent_merge(_p(scratch), segments, _p(out), tokens, heads, rank, _stream()), "latent_merge")
+        return out
     if tokens * heads <= LATENT_SPLIT_MAX_ROWS and ctx.max_kv_len > LATENT_SEGMENT:
         segments = -(-ctx.max_kv_len // LATENT_SEGMENT)
         scratch = _workspace(qk.device, tokens * heads * segments * (rank + 2))
-    _check(library().vosti_latent_attend(
+    _check(lib.vosti_latent_attend(
         _p(qk), _p(c_cache), _p(r_cache), _p(out), _p(ctx.positions), _p(ctx.request_of), _p(group.block_table),
         group.block_table.shape[1], group.page_size, num_pages, None, tokens, heads, rank, rot, ctypes.c_float(scale),
         window, _p(scratch), LATENT_SEGMENT, segments, flag, _p(ctx.status), _stream()), "latent_attend",
