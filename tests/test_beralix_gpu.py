@@ -489,6 +489,38 @@ def test_scan_state_of_a_slot_that_is_used_again_and_unequal_requests_in_one_ste
     assert int(harness.status.item()) == 0
 
 
+@pytest.mark.parametrize("states", [7, 48])
+def test_scan_portions_of_several_chunks_beside_short_ones_in_one_step(states):
+    """Portions longer than a block's chunk run as chunks side by side; their lengths here fall on,
+    just under and just over multiples of the chunk, beside a single token and a short portion."""
+    gen = torch.Generator().manual_seed(8 + states)
+    width, inner = 40, 70
+    mixer = build_mixer(scan_spec(inner, states, 3, 4), width, None)
+    W = weights_of(mixer, gen)
+    give(mixer, W, torch.float32)
+    m = dict(inner=inner, state=states, conv=3, dt_rank=4)
+    chunk = ops.library().vosti_scan_chunk(states)
+    lengths = {"a": 3 * chunk + 1, "b": 2 * chunk + 5, "c": 4 * chunk, "d": chunk + 9}
+    xs = {r: rounded(n, width, gen=gen) for r, n in lengths.items()}
+    want = {r: plain.selective_scan(x.double(), {k: v.double() for k, v in W.items()}, m).float() for r, x in xs.items()}
+    harness = Harness([None], [mixer.state_spec()], torch.float32, max_requests=4)
+    cache = harness.cache.layer_caches[0]
+    done = {r: 0 for r in xs}
+    def step(*parts):
+        ctx = harness.context([StepEntry(r, [0] * n) for r, n in parts])
+        rows = [xs[r][done[r]:done[r] + n] for r, n in parts]
+        got = ops.materialize(mixer.forward(ctx, torch.cat(rows).to(DEV), cache)).cpu()
+        exp = torch.cat([want[r][done[r]:done[r] + n] for r, n in parts])
+        assert torch.allclose(got, exp, **F32), (parts, float((got - exp).abs().max()))
+        for r, n in parts:
+            done[r] += n
+    step(("a", 2 * chunk), ("b", chunk + 4), ("d", 3))
+    step(("b", 1), ("a", chunk + 1), ("c", 4 * chunk), ("d", chunk - 1))         # a, c: whole chunks and one more token
+    step(("d", 7), ("b", chunk))
+    assert all(done[r] == lengths[r] for r in xs)
+    assert int(harness.status.item()) == 0
+
+
 # ---------------------------------------------------------------- whole models
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):

@@ -27,6 +27,12 @@ __device__ __forceinline__ float2 mean_inv(const float* row, int width, float ep
   return make_float2(mean, 1.f / sqrtf(var + eps));
 }
 
+// Loops over a row are written in batches of U elements a thread: all loads of a batch are issued
+// before its first store, because the row in shared memory, the stream and its (possibly same)
+// destination are plain pointers to the compiler and a load would otherwise wait for the store
+// before it, one memory latency per element.
+constexpr int U = 8;
+
 template <typename TO>
 __global__ void __launch_bounds__(256)
 layer_norm_stream_kernel(const float* stream, const void* y, int y_f32, const void* __restrict__ wy,
@@ -38,32 +44,64 @@ layer_norm_stream_kernel(const float* stream, const void* y, int y_f32, const vo
   pdl_wait();
   pdl_launch_dependents();
   const int64_t base = (int64_t)blockIdx.x * width;
+  const int step = blockDim.x;
+  float2 mi = make_float2(0.f, 1.f);
   if (y != nullptr) {
-    for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = load_flex(y, y_f32, base + i);
-    __syncthreads();
-    if (wy != nullptr) {
-      const float2 mi = mean_inv(row, width, eps_y, scratch);
-      for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float t = (row[i] - mi.x) * mi.y * load_flex(wy, wy_f32, i);
-        if (by != nullptr) t += load_flex(by, wy_f32, i);
-        if (sy != nullptr) t *= load_flex(sy, wy_f32, i);
-        row[i] = t;
-      }
+    for (int i0 = threadIdx.x; i0 < width; i0 += step * U) {
+      float v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = i0 + u * step < width ? load_flex(y, y_f32, base + i0 + u * step) : 0.f;
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * step < width) row[i0 + u * step] = v[u];
     }
-    if (stream != nullptr)
-      for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = stream[base + i] + row[i];
-  } else {
-    for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = stream[base + i];
+    __syncthreads();
+    if (wy != nullptr) mi = mean_inv(row, width, eps_y, scratch);
   }
-  if (stream_out != nullptr)
-    for (int i = threadIdx.x; i < width; i += blockDim.x) stream_out[base + i] = row[i];
+  // t = the term (normed and scaled, or as it is), x = stream + t -> row, stream_out
+  for (int i0 = threadIdx.x; i0 < width; i0 += step * U) {
+    float t[U], a[U], c[U], e[U], x[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * step;
+      const bool in = i < width;
+      x[u] = in && stream != nullptr ? stream[base + i] : 0.f;
+      a[u] = in && wy != nullptr ? load_flex(wy, wy_f32, i) : 1.f;
+      c[u] = in && wy != nullptr && by != nullptr ? load_flex(by, wy_f32, i) : 0.f;
+      e[u] = in && wy != nullptr && sy != nullptr ? load_flex(sy, wy_f32, i) : 1.f;
+      t[u] = in && y != nullptr ? row[i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * step;
+      if (i >= width) continue;
+      float term = t[u];
+      if (wy != nullptr) {
+        term = (term - mi.x) * mi.y * a[u];
+        if (by != nullptr) term += c[u];
+        if (sy != nullptr) term *= e[u];
+      }
+      const float sum = y == nullptr ? x[u] : stream != nullptr ? x[u] + term : term;
+      row[i] = sum;
+      if (stream_out != nullptr) stream_out[base + i] = sum;
+    }
+  }
   if (out == nullptr) return;
   __syncthreads();
-  const float2 mi = mean_inv(row, width, eps, scratch);
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = (row[i] - mi.x) * mi.y * load_flex(w, w_f32, i);
-    if (b != nullptr) v += load_flex(b, w_f32, i);
-    out[base + i] = from_f32<TO>(v);
+  mi = mean_inv(row, width, eps, scratch);
+  for (int i0 = threadIdx.x; i0 < width; i0 += step * U) {
+    float a[U], c[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * step;
+      a[u] = i < width ? load_flex(w, w_f32, i) : 0.f;
+      c[u] = i < width && b != nullptr ? load_flex(b, w_f32, i) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * step;
+      if (i < width) out[base + i] = from_f32<TO>((row[i] - mi.x) * mi.y * a[u] + c[u]);
+    }
   }
 }
 

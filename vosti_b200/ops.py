@@ -1066,10 +1066,18 @@ def scan_run(x: torch.Tensor, dtp: torch.Tensor, dt_bias: Optional[torch.Tensor]
         raise KernelError("scan_run: shapes do not fit")
     y = torch.empty_like(x)
     z = xz[:, inner:]
+    chunk = library().vosti_scan_chunk(states)
+    ws = ws_dt = None
+    several = ctx.max_q_len > chunk
+    if several:                  # chunks of a long portion run side by side: start states and step-size sums per chunk
+        places = x.shape[0] // chunk + ctx.num_requests
+        ws = torch.empty((places, inner, states), dtype=torch.float32, device=x.device)
+        ws_dt = torch.empty((places, inner), dtype=torch.float32, device=x.device)
     _check(library().vosti_scan_run(
         _p(x), _p(dtp), _p(dt_bias), _p(bc), _p(a_log), _p(d_skip), _is_f32(a_log), _p(z), ctypes.c_int64(xz.shape[1]),
         _p(state), ctypes.c_int64(state.shape[1]), _p(ctx.cu_q), _p(ctx.state_slots), state.shape[0], ctx.num_requests,
-        inner, states, _p(y), _is_f32(x), _p(ctx.status), _stream()), "scan_run")
+        ctx.max_q_len, inner, states, _p(ws), _p(ws_dt), _p(y), _is_f32(x), _p(ctx.status), _stream()), "scan_run",
+        kernels=3 if several else 1)
     return y
 
 
