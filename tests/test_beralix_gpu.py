@@ -98,7 +98,7 @@ CUTS = lambda T: ((T,), (T - 33,) + (1,) * 33, (2, 5, 1, 1, 17, 2, 3, T - 31))
 
 # ---------------------------------------------------------------- layer norm over the stream
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width", [200, 67, 1])
+@pytest.mark.parametrize("width", [200, 67, 1, 4, 1024, 1028, 2600, 6148, 8196])      # rows in registers up to 8192, else shared memory
 def test_layer_norm_of_the_stream_with_a_normed_scaled_term(dtype, width):
     gen = torch.Generator().manual_seed(width)
     rows, eps = 9, 3e-6

@@ -272,8 +272,12 @@ latent_attend_kernel(const T* __restrict__ qk, const T* __restrict__ c_cache, co
   }
 }
 
-// A row's segments in segment order, then the division.
-template <int RW>
+// A row's segments joined: the largest of the segments' maxima first (lanes over segments), then
+// every segment's sums weighted by 2^(its maximum - the largest) and added in segment order, then
+// the division. A warp takes 128 elements of a row (blockIdx.y says which), so that the loads of
+// a segment do not wait for the segment before it and few rows still fill the GPU.
+constexpr int MERGE_SLICE = 128;
+
 __global__ void __launch_bounds__(WARPS * 32)
 latent_merge_kernel(const float* __restrict__ partial, int segments, float* __restrict__ out,
                     const int* __restrict__ token_list, int tokens, int heads, int rank) {
@@ -283,29 +287,36 @@ latent_merge_kernel(const float* __restrict__ partial, int segments, float* __re
   const int64_t wid = (int64_t)blockIdx.x * WARPS + warp;
   if (wid >= (int64_t)tokens * heads) return;
   const int t = token_list != nullptr ? token_list[wid / heads] : (int)(wid / heads), h = (int)(wid % heads);
-  float m = -INFINITY, l = 0.f;
-  float acc[RW];
+  const float* row = partial + wid * segments * (int64_t)(rank + 2);
+  float top = -INFINITY;
+  for (int s = lane; s < segments; s += 32) top = fmaxf(top, row[(int64_t)s * (rank + 2)]);
 #pragma unroll
-  for (int i = 0; i < RW; ++i) acc[i] = 0.f;
-  for (int s = 0; s < segments; ++s) {
-    const float* rec = partial + (wid * segments + s) * (int64_t)(rank + 2);
-    const float ms = rec[0], ls = rec[1];
-    if (ms == -INFINITY) continue;
-    const float m_new = fmaxf(m, ms);
-    const float a = exp2f(m - m_new), c = exp2f(ms - m_new);
-    l = l * a + ls * c;
+  for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+  const int first = blockIdx.y * MERGE_SLICE;
+  float l = 0.f;
+  float acc[MERGE_SLICE / 32];
 #pragma unroll
-    for (int i = 0; i < RW; ++i) {
-      const int idx = lane + 32 * i;
-      if (idx < rank) acc[i] = acc[i] * a + rec[2 + idx] * c;
+  for (int i = 0; i < MERGE_SLICE / 32; ++i) acc[i] = 0.f;
+  if (top != -INFINITY) {
+#pragma unroll 4
+    for (int s = 0; s < segments; ++s) {
+      const float* rec = row + (int64_t)s * (rank + 2);
+      const float ms = rec[0];
+      if (ms == -INFINITY) continue;                  // a segment without a visible key left no sums
+      const float c = exp2f(ms - top);
+      l = fmaf(rec[1], c, l);
+#pragma unroll
+      for (int i = 0; i < MERGE_SLICE / 32; ++i) {
+        const int idx = first + lane + 32 * i;
+        if (idx < rank) acc[i] = fmaf(rec[2 + idx], c, acc[i]);
+      }
     }
-    m = m_new;
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
   float* orow = out + ((int64_t)t * heads + h) * rank;
 #pragma unroll
-  for (int i = 0; i < RW; ++i) {
-    const int idx = lane + 32 * i;
+  for (int i = 0; i < MERGE_SLICE / 32; ++i) {
+    const int idx = first + lane + 32 * i;
     if (idx < rank) orow[idx] = acc[i] * inv;
   }
 }
@@ -422,8 +433,8 @@ VOSTI_API int vosti_latent_attend(const void* qk, const void* c_cache, const voi
     if (segments > 1) {                                                                                                 \
       cudaError_t e = cudaGetLastError();                                                                               \
       if (e != cudaSuccess) { vosti_set_error("%s", cudaGetErrorString(e)); return (int)e; }                            \
-      vosti_launch(latent_merge_kernel<RW>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, (const float*)partial, \
-                   segments, out, token_list, tokens, heads, rank);                                                     \
+      vosti_launch(latent_merge_kernel, dim3((unsigned)blocks, (rank + MERGE_SLICE - 1) / MERGE_SLICE), dim3(WARPS * 32), 0, \
+                   stream, (const float*)partial, segments, out, token_list, tokens, heads, rank);                      \
     }                                                                                                                   \
   } while (0)
   if (rw == 4) VOSTI_LA(4);
@@ -443,10 +454,7 @@ VOSTI_API int vosti_latent_merge(const float* partial, int segments, float* out,
   if (tokens == 0) return VOSTI_OK;
   const int64_t blocks = ((int64_t)tokens * heads + WARPS - 1) / WARPS;
   VOSTI_REQUIRE(blocks <= 0x7fffffffLL, "latent_merge: too many (token, head) pairs");
-  const dim3 grid((unsigned)blocks), block(WARPS * 32);
-  if (rank <= 128) vosti_launch(latent_merge_kernel<4>, grid, block, 0, stream, partial, segments, out, (const int*)nullptr, tokens, heads, rank);
-  else if (rank <= 256) vosti_launch(latent_merge_kernel<8>, grid, block, 0, stream, partial, segments, out, (const int*)nullptr, tokens, heads, rank);
-  else if (rank <= 512) vosti_launch(latent_merge_kernel<16>, grid, block, 0, stream, partial, segments, out, (const int*)nullptr, tokens, heads, rank);
-  else vosti_launch(latent_merge_kernel<32>, grid, block, 0, stream, partial, segments, out, (const int*)nullptr, tokens, heads, rank);
+  const dim3 grid((unsigned)blocks, (rank + MERGE_SLICE - 1) / MERGE_SLICE), block(WARPS * 32);
+  vosti_launch(latent_merge_kernel, grid, block, 0, stream, partial, segments, out, (const int*)nullptr, tokens, heads, rank);
   VOSTI_LAUNCH_CHECK();
 }
