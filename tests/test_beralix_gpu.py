@@ -282,6 +282,44 @@ def test_a_window_passes_over_decoded_tokens_and_its_pages_come_back():
     assert harness.cache.available_pages() == window // page + 4
 
 
+# ---------------------------------------------------------------- the per-head product
+@pytest.mark.parametrize("tokens", [1, 7, 16, 17, 150])
+@pytest.mark.parametrize("x_type,y_type", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.bfloat16),
+                                           (torch.float32, torch.float32), (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("inner,outer,contiguous", [(24, 40, "out"), (40, 24, "in"), (136, 200, "in"), (72, 264, "out"),
+                                                    (12, 20, "out"), (10, 6, "in")])
+def test_head_project_against_einsum(tokens, x_type, y_type, inner, outer, contiguous):
+    """y[t, h] = g[t, h] (x[t, h] M_h) for a bfloat16 M_h stored with either axis contiguous, x and y
+    strided views of wider rows; sizes in multiples of 8 take the tensor cores, the others the CUDA
+    cores. A float32 x keeps 16 bits of its mantissa."""
+    gen = torch.Generator().manual_seed(tokens * 131 + inner)
+    heads, pad = 3, 8
+    x_wide = torch.randn(tokens, heads, inner + pad, generator=gen)
+    if x_type == torch.bfloat16:
+        x_wide = x_wide.to(torch.bfloat16).float()
+    else:
+        x_wide = (x_wide.to(torch.bfloat16).float() * (1.0 + 2.0 ** -9))          # needs more than 8 bits
+    m = rounded(heads, inner, outer, gen=gen, std=1.0 / math.sqrt(inner))
+    gate = torch.rand(tokens, heads, generator=gen)
+    want = torch.einsum("thi,hio->tho", x_wide[..., :inner].double(), m.double()) * gate.double()[..., None]
+    xd = x_wide.to(DEV, x_type)[..., :inner]
+    if contiguous == "out":
+        md = m.to(DEV, torch.bfloat16).contiguous()
+    else:
+        md = m.transpose(1, 2).to(DEV, torch.bfloat16).contiguous().transpose(1, 2)
+    y_wide = torch.zeros(tokens, heads, outer + pad, dtype=y_type, device=DEV)
+    ops.head_project(xd, md, y_wide[..., :outer], gate=gate.to(DEV))
+    torch.cuda.synchronize()
+    got = y_wide[..., :outer].double().cpu()
+    bound = 2e-5 if y_type == torch.float32 else 6e-3
+    assert (got - want).abs().max() <= bound * max(1.0, want.abs().max().item())
+    assert y_wide[..., outer:].abs().max().item() == 0.0
+    without = torch.zeros(tokens, heads, outer, dtype=y_type, device=DEV)
+    ops.head_project(xd, md, without)
+    ungated = torch.einsum("thi,hio->tho", x_wide[..., :inner].double(), m.double())
+    assert (without.double().cpu() - ungated).abs().max() <= bound * max(1.0, ungated.abs().max().item())
+
+
 # ---------------------------------------------------------------- latent attention
 def latent_block(heads, dim, rot, dv, rank, scale, base, scaling):
     return dict(heads=heads, dim=dim, rot_dim=rot, vdim=dv, kv_rank=rank, scale=scale, rot=dict(base=base, dims=rot, scaling=scaling))

@@ -146,24 +146,38 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
     const int key0 = tile_begin + tile * LKT;
 
     // ---- scores of the warp's 8 keys against all rows
-    float s[MT][4];
+    // four separate running sums a row tile (two per step, alternating steps), so that an mma does not wait
+    // for the one before it; they meet once the key is through
+    float s[MT][4], sa[MT][4], sb[MT][4], sc[MT][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) s[mt][0] = s[mt][1] = s[mt][2] = s[mt][3] = 0.f;
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[mt][e] = sa[mt][e] = sb[mt][e] = sc[mt][e] = 0.f;
     const uint32_t k_lane = smem_addr(ks + (warp * 8 + (lane & 7)) * pitch + (lane >> 3) * 16);
     const uint32_t q_lane = smem_addr(q_s + (lane & 15) * pitch + (lane >> 4) * 16);
-#pragma unroll 2
-    for (int kk = 0; kk < kw / 32; ++kk) {       // 32 elements of the key a step: two mma k-steps
+    auto step = [&](int kk, float (&first)[MT][4], float (&second)[MT][4]) {       // 32 elements of the key: two mma k-steps
       uint32_t bm[4];
       ldmatrix_x4(bm, k_lane + kk * 64);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        uint32_t a[4];
+        uint32_t a[4], a2[4];
         ldmatrix_x4(a, q_lane + mt * 16 * pitch + kk * 64);
-        mma_bf16(s[mt], a, bm[0], bm[1]);
-        ldmatrix_x4(a, q_lane + mt * 16 * pitch + kk * 64 + 32);
-        mma_bf16(s[mt], a, bm[2], bm[3]);
+        ldmatrix_x4(a2, q_lane + mt * 16 * pitch + kk * 64 + 32);
+        mma_bf16(first[mt], a, bm[0], bm[1]);
+        mma_bf16(second[mt], a2, bm[2], bm[3]);
       }
+    };
+    const int key_steps = kw / 32;
+    int kk = 0;
+    for (; kk + 1 < key_steps; kk += 2) {
+      step(kk, s, sa);
+      step(kk + 1, sb, sc);
     }
+    if (kk < key_steps) step(kk, s, sa);
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[mt][e] = (s[mt][e] + sa[mt][e]) + (sb[mt][e] + sc[mt][e]);
     // ---- mask, scale, the tile's row maxima across the warps
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
@@ -281,6 +295,152 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
     }
 }
 
+__device__ __forceinline__ void store_pair(float* at, float a, float b) { *reinterpret_cast<float2*>(at) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(bf16* at, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(at) = __floats2bfloat162_rn(a, b); }
+
+// ---- y[t, h, :] = g[t, h] * (x[t, h, :] @ M_h) on the tensor cores: one small product per head.
+// A CTA takes 16 WM tokens x 8 NT WN outputs of one head; the inner extent passes through shared
+// memory 64 elements at a time while the next piece is already on its way in registers. M_h is
+// read where it lies: rows of outputs with the inner index contiguous (KMAJOR) or rows of inner
+// elements with the output index contiguous. A float32 x enters as two bfloat16 terms, x = hi + lo,
+// so that the product sees 16 bits of its mantissa.
+constexpr int HPK = 64;
+
+template <bool XF32, bool KMAJOR, int WM, int WN, int NT, typename TY>
+__global__ void __launch_bounds__(WM * WN * 32)
+head_project_mma_kernel(const void* __restrict__ x_, int64_t x_row, int64_t x_head, const bf16* __restrict__ m,
+                        int64_t m_head, int64_t m_stride, const float* __restrict__ gate, TY* __restrict__ y,
+                        int64_t y_row, int64_t y_head, int tokens, int heads, int in, int out) {
+  constexpr int THREADS = WM * WN * 32, TM = 16 * WM, TN = 8 * NT * WN;
+  constexpr int A_PITCH = HPK + 8;
+  constexpr int B_ROWS = KMAJOR ? TN : HPK, B_COLS = KMAJOR ? HPK : TN, B_PITCH = B_COLS + 8;
+  constexpr int AV = TM * (HPK / 8) / THREADS, BV = B_ROWS * (B_COLS / 8) / THREADS;
+  static_assert(AV >= 1 && BV >= 1 && NT % 2 == 0, "head_project_mma: tile shape");
+  __shared__ __align__(16) bf16 a_s[XF32 ? 2 : 1][TM][A_PITCH];
+  __shared__ __align__(16) bf16 b_s[B_ROWS][B_PITCH];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = warp % WM, wn = warp / WM;
+  const int h = blockIdx.y, t0 = blockIdx.z * TM, o0 = blockIdx.x * TN;
+  const bf16* mh = m + (int64_t)h * m_head;
+
+  uint4 a_reg[AV][XF32 ? 2 : 1], b_reg[BV];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int v = 0; v < AV; ++v) {
+      const int idx = tid + v * THREADS, r = idx / (HPK / 8), c = idx % (HPK / 8);
+      const int t = t0 + r, k = k0 + c * 8;
+      const bool valid = t < tokens && k < in;
+      if (XF32) {
+        const float* src = reinterpret_cast<const float*>(x_) + (int64_t)t * x_row + (int64_t)h * x_head + k;
+        a_reg[v][0] = valid ? *reinterpret_cast<const uint4*>(src) : make_uint4(0, 0, 0, 0);
+        a_reg[v][XF32 ? 1 : 0] = valid ? *reinterpret_cast<const uint4*>(src + 4) : make_uint4(0, 0, 0, 0);
+      } else {
+        const bf16* src = reinterpret_cast<const bf16*>(x_) + (int64_t)t * x_row + (int64_t)h * x_head + k;
+        a_reg[v][0] = valid ? *reinterpret_cast<const uint4*>(src) : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < BV; ++v) {
+      const int idx = tid + v * THREADS, r = idx / (B_COLS / 8), c = idx % (B_COLS / 8);
+      const int k = KMAJOR ? k0 + c * 8 : k0 + r, o = KMAJOR ? o0 + r : o0 + c * 8;
+      const bf16* src = mh + (KMAJOR ? (int64_t)o * m_stride + k : (int64_t)k * m_stride + o);
+      b_reg[v] = (k < in && o < out) ? *reinterpret_cast<const uint4*>(src) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  auto stage = [&]() {
+#pragma unroll
+    for (int v = 0; v < AV; ++v) {
+      const int idx = tid + v * THREADS, r = idx / (HPK / 8), c = idx % (HPK / 8);
+      if (XF32) {
+        const float* f0 = reinterpret_cast<const float*>(&a_reg[v][0]);
+        const float* f1 = reinterpret_cast<const float*>(&a_reg[v][XF32 ? 1 : 0]);
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float u0 = e < 2 ? f0[2 * e] : f1[2 * e - 4], u1 = e < 2 ? f0[2 * e + 1] : f1[2 * e - 3];
+          const __nv_bfloat162 top = __floats2bfloat162_rn(u0, u1);
+          const float2 back = __bfloat1622float2(top);
+          hi[e] = *reinterpret_cast<const uint32_t*>(&top);
+          lo[e] = pack_bf16(u0 - back.x, u1 - back.y);
+        }
+        *reinterpret_cast<uint4*>(&a_s[0][r][c * 8]) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(&a_s[XF32 ? 1 : 0][r][c * 8]) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      } else {
+        *reinterpret_cast<uint4*>(&a_s[0][r][c * 8]) = a_reg[v][0];
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < BV; ++v) {
+      const int idx = tid + v * THREADS, r = idx / (B_COLS / 8), c = idx % (B_COLS / 8);
+      *reinterpret_cast<uint4*>(&b_s[r][c * 8]) = b_reg[v];
+    }
+  };
+
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  const int n_warp = wn * NT * 8;                // the warp's first output column of the tile
+
+  fetch(0);
+  for (int k0 = 0; k0 < in; k0 += HPK) {
+    __syncthreads();
+    stage();
+    __syncthreads();
+    if (k0 + HPK < in) fetch(k0 + HPK);
+#pragma unroll
+    for (int kk = 0; kk < HPK / 32; ++kk) {      // 32 inner elements a step: two mma k-steps
+      uint32_t a_hi[2][4], a_lo[2][4];
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        ldmatrix_x4(a_hi[s], smem_addr(&a_s[0][wm * 16 + (lane & 15)][kk * 32 + s * 16 + (lane >> 4) * 8]));
+        if (XF32) ldmatrix_x4(a_lo[s], smem_addr(&a_s[XF32 ? 1 : 0][wm * 16 + (lane & 15)][kk * 32 + s * 16 + (lane >> 4) * 8]));
+      }
+      if (KMAJOR) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          uint32_t bm[4];
+          ldmatrix_x4(bm, smem_addr(&b_s[n_warp + nt * 8 + (lane & 7)][kk * 32 + (lane >> 3) * 8]));
+          mma_bf16(acc[nt], a_hi[0], bm[0], bm[1]);
+          mma_bf16(acc[nt], a_hi[1], bm[2], bm[3]);
+          if (XF32) {
+            mma_bf16(acc[nt], a_lo[0], bm[0], bm[1]);
+            mma_bf16(acc[nt], a_lo[1], bm[2], bm[3]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+#pragma unroll
+          for (int n2 = 0; n2 < NT / 2; ++n2) {
+            uint32_t bm[4];
+            ldmatrix_x4_trans(bm, smem_addr(&b_s[kk * 32 + s * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][n_warp + n2 * 16 + (lane >> 4) * 8]));
+            mma_bf16(acc[2 * n2], a_hi[s], bm[0], bm[1]);
+            mma_bf16(acc[2 * n2 + 1], a_hi[s], bm[2], bm[3]);
+            if (XF32) {
+              mma_bf16(acc[2 * n2], a_lo[s], bm[0], bm[1]);
+              mma_bf16(acc[2 * n2 + 1], a_lo[s], bm[2], bm[3]);
+            }
+          }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int t = t0 + wm * 16 + (lane >> 2) + 8 * r;
+    if (t >= tokens) continue;
+    const float g = gate != nullptr ? gate[(int64_t)t * heads + h] : 1.f;
+    TY* dst = y + (int64_t)t * y_row + (int64_t)h * y_head;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int o = o0 + n_warp + nt * 8 + (lane & 3) * 2;
+      if (o >= out) continue;
+      store_pair(dst + o, acc[nt][2 * r] * g, acc[nt][2 * r + 1] * g);
+    }
+  }
+}
+
 size_t latent_mma_smem(int rank, int rot, int mt) {
   const size_t pitch = (size_t)(rank + rot) * 2 + 16;
   return (16 * mt + 2 * LKT) * pitch + 2 * 16 * mt * P_PITCH + LW * 16 * mt * sizeof(float);
@@ -330,5 +490,54 @@ VOSTI_API int vosti_latent_attend_mma(const void* qk, const void* c_cache, const
   else if (rank == 256) { if (mt == 2) VOSTI_LM(256, 2); else VOSTI_LM(256, 1); }
   else { if (mt == 2) VOSTI_LM(128, 2); else VOSTI_LM(128, 1); }
 #undef VOSTI_LM
+  VOSTI_LAUNCH_CHECK();
+}
+
+// y[t, h, o] = gate[t, h] * sum_i x[t, h, i] * m[h * m_head + i * m_in + o * m_out] with a bfloat16 m
+// whose inner or output index is contiguous (m_in == 1 or m_out == 1), on the tensor cores. The
+// caller has checked vosti_head_project_mma_fits. x and y float32 or bfloat16; strides in elements.
+VOSTI_API int vosti_head_project_mma_fits(int64_t x_row, int64_t x_head, int x_f32, int64_t m_head, int64_t m_in,
+                                          int64_t m_out, int64_t y_row, int64_t y_head, int in, int out) {
+  const int xv = x_f32 ? 4 : 8;
+  const int64_t m_stride = m_in == 1 ? m_out : m_in;
+  return (m_in == 1 || m_out == 1) && in % 8 == 0 && out % 8 == 0 && x_row % xv == 0 && x_head % xv == 0 &&
+         m_head % 8 == 0 && m_stride % 8 == 0 && y_row % 2 == 0 && y_head % 2 == 0;
+}
+
+VOSTI_API int vosti_head_project_mma(const void* x, int x_f32, int64_t x_row, int64_t x_head, const void* m,
+                                     int64_t m_head, int64_t m_in, int64_t m_out, const float* gate, void* y, int y_f32,
+                                     int64_t y_row, int64_t y_head, int tokens, int heads, int in, int out,
+                                     cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && heads > 0 && heads <= 65535 && in > 0 && out > 0, "head_project_mma: bad sizes");
+  VOSTI_REQUIRE(vosti_head_project_mma_fits(x_row, x_head, x_f32, m_head, m_in, m_out, y_row, y_head, in, out),
+                "head_project_mma: strides or sizes this kernel does not take");
+  VOSTI_REQUIRE((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(m)) % 16 == 0 &&
+                reinterpret_cast<uintptr_t>(y) % 8 == 0, "head_project_mma: operands are not aligned");
+  if (tokens == 0) return VOSTI_OK;
+  const bool kmajor = m_in == 1;
+  const int64_t m_stride = kmajor ? m_out : m_in;
+  const bool few = tokens <= 16;
+  const int tm = few ? 16 : 64, tn = few ? 64 : 128;
+  const int token_tiles = (tokens + tm - 1) / tm;
+  VOSTI_REQUIRE(token_tiles <= 65535, "head_project_mma: too many tokens for one launch");
+  const dim3 grid((out + tn - 1) / tn, heads, token_tiles);
+#define VOSTI_HPM(XF, KM, WM, WN, NT, TY)                                                                          \
+  vosti_launch(head_project_mma_kernel<XF, KM, WM, WN, NT, TY>, grid, dim3(WM * WN * 32), 0, stream, x, x_row,     \
+               x_head, (const bf16*)m, m_head, m_stride, gate, (TY*)y, y_row, y_head, tokens, heads, in, out)
+#define VOSTI_HPM_SHAPE(XF, KM, TY)                                                                                \
+  do {                                                                                                             \
+    if (few) VOSTI_HPM(XF, KM, 1, 4, 2, TY);                                                                       \
+    else VOSTI_HPM(XF, KM, 4, 2, 8, TY);                                                                           \
+  } while (0)
+#define VOSTI_HPM_TYPES(XF, KM)                                                                                    \
+  do {                                                                                                             \
+    if (y_f32) VOSTI_HPM_SHAPE(XF, KM, float);                                                                     \
+    else VOSTI_HPM_SHAPE(XF, KM, bf16);                                                                            \
+  } while (0)
+  if (x_f32) { if (kmajor) VOSTI_HPM_TYPES(true, true); else VOSTI_HPM_TYPES(true, false); }
+  else { if (kmajor) VOSTI_HPM_TYPES(false, true); else VOSTI_HPM_TYPES(false, false); }
+#undef VOSTI_HPM_TYPES
+#undef VOSTI_HPM_SHAPE
+#undef VOSTI_HPM
   VOSTI_LAUNCH_CHECK();
 }

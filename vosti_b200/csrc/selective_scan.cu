@@ -24,30 +24,35 @@ namespace {
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
+// A thread takes one channel (neighbouring threads neighbouring channels) and `per_block` tokens one
+// after the other, so that the taps' weights and the inputs a token shares with the one before it
+// come from the first-level cache.
 template <typename T>
 __global__ void __launch_bounds__(256)
 scan_conv_kernel(const T* __restrict__ xz, int64_t xz_stride, const void* __restrict__ conv_w, const void* __restrict__ conv_b,
                  int w_f32, const float* state, int64_t state_stride, int64_t tail_offset, const int* __restrict__ request_of,
                  const int* __restrict__ cu_q, const int* __restrict__ state_slots, int num_slots, int inner, int taps,
-                 T* __restrict__ out, unsigned* status) {
+                 int tokens, int per_block, T* __restrict__ out, unsigned* status) {
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x;
-  const int b = request_of[t];
-  const int first = cu_q[b], slot = state_slots[b];
-  if (slot < 0 || slot >= num_slots) {
-    if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
-    return;
-  }
-  const float* tail = state + (int64_t)slot * state_stride + tail_offset;          // [taps - 1, inner]
-  const int back = t - first;                                                       // tokens of the portion before this one
-  for (int c = threadIdx.x; c < inner; c += blockDim.x) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int t_end = min(tokens, ((int)blockIdx.y + 1) * per_block);
+  for (int t = blockIdx.y * per_block; t < t_end; ++t) {
+    const int b = request_of[t];
+    const int first = cu_q[b], slot = state_slots[b];
+    if (slot < 0 || slot >= num_slots) {
+      if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
+      continue;
+    }
+    if (c >= inner) continue;
+    const float* tail = state + (int64_t)slot * state_stride + tail_offset;          // [taps - 1, inner]
+    const int back = t - first;                                                       // tokens of the portion before this one
     float acc = conv_b != nullptr ? load_flex(conv_b, w_f32, c) : 0.f;
     for (int j = 0; j < taps; ++j) {
-      const int ago = taps - 1 - j;                                                 // tap j reads the input `ago` tokens back
+      const int ago = taps - 1 - j;                                                   // tap j reads the input `ago` tokens back
       float u;
       if (ago <= back) u = to_f32(xz[(int64_t)(t - ago) * xz_stride + c]);
-      else u = tail[(int64_t)(taps - 1 - (ago - back)) * inner + c];                // the tail's last row is the newest
+      else u = tail[(int64_t)(taps - 1 - (ago - back)) * inner + c];                  // the tail's last row is the newest
       acc = fmaf(load_flex(conv_w, w_f32, (int64_t)c * taps + j), u, acc);
     }
     out[(int64_t)t * inner + c] = from_f32<T>(silu_f(acc));
@@ -227,14 +232,20 @@ VOSTI_API int vosti_scan_conv(const void* xz, int64_t xz_stride, const void* con
                               int is_f32, unsigned* status, cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && requests >= 0 && inner > 0 && taps >= 1 && taps <= 64, "scan_conv: bad sizes");
   if (tokens == 0) return VOSTI_OK;
+  const int across_c = (inner + 255) / 256;
+  int per_block = 1;                      // tokens a block takes: more once the grid fills the GPU several times over
+  while (per_block < 16 && (int64_t)across_c * ((tokens + per_block - 1) / per_block) > 148 * 16) per_block *= 2;
+  const int token_blocks = (tokens + per_block - 1) / per_block;
+  VOSTI_REQUIRE(token_blocks <= 65535, "scan_conv: too many tokens for one launch");
+  const dim3 grid(across_c, token_blocks);
   if (is_f32)
-    vosti_launch(scan_conv_kernel<float>, dim3(tokens), dim3(256), 0, stream, (const float*)xz, xz_stride, conv_w, conv_b, w_f32,
+    vosti_launch(scan_conv_kernel<float>, grid, dim3(256), 0, stream, (const float*)xz, xz_stride, conv_w, conv_b, w_f32,
                  (const float*)state, state_stride, tail_offset, request_of, cu_q, state_slots, num_slots, inner, taps,
-                 (float*)out, status);
+                 tokens, per_block, (float*)out, status);
   else
-    vosti_launch(scan_conv_kernel<bf16>, dim3(tokens), dim3(256), 0, stream, (const bf16*)xz, xz_stride, conv_w, conv_b, w_f32,
+    vosti_launch(scan_conv_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)xz, xz_stride, conv_w, conv_b, w_f32,
                  (const float*)state, state_stride, tail_offset, request_of, cu_q, state_slots, num_slots, inner, taps,
-                 (bf16*)out, status);
+                 tokens, per_block, (bf16*)out, status);
   if (taps > 1) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { vosti_set_error("%s", cudaGetErrorString(e)); return (int)e; }

@@ -971,16 +971,31 @@ def latent_prep(proj: torch.Tensor, qk: torch.Tensor, c_cache: Optional[torch.Te
 
 
 def head_project(x: torch.Tensor, m: torch.Tensor, y: torch.Tensor, *, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y[t, h, :] = gate[t, h] * (x[t, h, :] @ m[h]) on the CUDA cores, float32 arithmetic. x [tokens,
-    heads, in], m [heads, in, out] and y [tokens, heads, out] may be strided views (unit stride
-    along x's and y's last axis); gate float32 [tokens, heads]."""
+    """y[t, h, :] = gate[t, h] * (x[t, h, :] @ m[h]) with float32 sums. x [tokens, heads, in],
+    m [heads, in, out] and y [tokens, heads, out] may be strided views (unit stride along x's and
+    y's last axis); gate float32 [tokens, heads]. A bfloat16 m with a contiguous inner or output
+    axis and strides in multiples of 8 runs on the tensor cores (a float32 x as two bfloat16
+    terms); everything else on the CUDA cores in float32."""
     tokens, heads, inner = x.shape
     if tuple(m.shape[:2]) != (heads, inner) or tuple(y.shape) != (tokens, heads, m.shape[2]):
         raise KernelError("head_project: shapes do not fit")
     if tokens and (x.stride(2) != 1 or y.stride(2) != 1):
         raise KernelError("head_project: the last axis of x and y must be contiguous")
     _contig(gate)
-    _check(library().vosti_head_project(
+    lib = library()
+    if (tokens and m.dtype == torch.bfloat16 and x.dtype in (torch.bfloat16, torch.float32)
+            and y.dtype in (torch.bfloat16, torch.float32) and x.data_ptr() % 16 == 0 and m.data_ptr() % 16 == 0
+            and y.data_ptr() % 8 == 0
+            and lib.vosti_head_project_mma_fits(ctypes.c_int64(x.stride(0)), ctypes.c_int64(x.stride(1)), _is_f32(x),
+                                                ctypes.c_int64(m.stride(0)), ctypes.c_int64(m.stride(1)),
+                                                ctypes.c_int64(m.stride(2)), ctypes.c_int64(y.stride(0)),
+                                                ctypes.c_int64(y.stride(1)), inner, m.shape[2])):
+        _check(lib.vosti_head_project_mma(
+            _p(x), _is_f32(x), ctypes.c_int64(x.stride(0)), ctypes.c_int64(x.stride(1)), _p(m), ctypes.c_int64(m.stride(0)),
+            ctypes.c_int64(m.stride(1)), ctypes.c_int64(m.stride(2)), _p(gate), _p(y), _is_f32(y), ctypes.c_int64(y.stride(0)),
+            ctypes.c_int64(y.stride(1)), tokens, heads, inner, m.shape[2], _stream()), "head_project_mma")
+        return y
+    _check(lib.vosti_head_project(
         _p(x), _is_f32(x), ctypes.c_int64(x.stride(0)), ctypes.c_int64(x.stride(1)), _p(m), _is_f32(m),
         ctypes.c_int64(m.stride(0)), ctypes.c_int64(m.stride(1)), ctypes.c_int64(m.stride(2)), _p(gate), _p(y), _is_f32(y),
         ctypes.c_int64(y.stride(0)), ctypes.c_int64(y.stride(1)), tokens, heads, inner, m.shape[2], _stream()), "head_project")
