@@ -97,20 +97,23 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
   auto issue = [&](int tile, int buffer) {
     const int key0 = tile_begin + tile * LKT;
     uint8_t* dst = k_s + buffer * (LKT * pitch);
-    for (int r = warp; r < LKT; r += LW) {
-      const int key = key0 + r;
-      bool valid = key >= first_key && key < key_end;
-      int64_t slot = 0;
-      if (valid) {
+    // lane i looks up the slot of the warp's i-th row; the rows then take it from there
+    int64_t my_slot = -1;
+    if (lane < LKT / LW) {
+      const int key = key0 + warp + lane * LW;
+      if (key >= first_key && key < key_end) {
         const int index = key / page_size;
         const int page = index < max_pages ? table[index] : -1;
-        if (page < 0 || page >= num_pages) {
-          if (lane == 0) raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
-          valid = false;
-        } else {
-          slot = (int64_t)page * page_size + (key - index * page_size);
-        }
+        if (page < 0 || page >= num_pages) raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
+        else my_slot = (int64_t)page * page_size + (key - index * page_size);
       }
+    }
+#pragma unroll
+    for (int i = 0; i < LKT / LW; ++i) {
+      const int r = warp + i * LW;
+      int64_t slot = __shfl_sync(0xffffffffu, my_slot, i);
+      const bool valid = slot >= 0;
+      if (!valid) slot = 0;
       const bf16* crow = c_cache + slot * RANK;
       const bf16* rrow = r_cache + slot * rot;
       for (int c = lane; c < chunks; c += 32) {
@@ -209,9 +212,9 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
         for (int w = 0; w < LW; ++w) tile_max = fmaxf(tile_max, red_s[w * ROWS + row]);
         const float m_new = fmaxf(m_row[mt][r], tile_max);
         const float safe = m_new == -INFINITY ? 0.f : m_new;
-        alpha[r] = exp2f(m_row[mt][r] - safe);
+        alpha[r] = fast_exp2(m_row[mt][r] - safe);
         m_row[mt][r] = m_new;
-        const float p0 = exp2f(s[mt][2 * r] - safe), p1 = exp2f(s[mt][2 * r + 1] - safe);
+        const float p0 = fast_exp2(s[mt][2 * r] - safe), p1 = fast_exp2(s[mt][2 * r + 1] - safe);
         l_row[mt][r] = l_row[mt][r] * alpha[r] + p0 + p1;              // this thread's keys only; joined at the end
         const __nv_bfloat162 hi = __floats2bfloat162_rn(p0, p1);
         const float2 back = __bfloat1622float2(hi);
@@ -239,18 +242,25 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
         ldmatrix_x4(hi[mt], p_lane + mt * 16 * P_PITCH + j * 32);
         ldmatrix_x4(lo[mt], p_lane + (ROWS + mt * 16) * P_PITCH + j * 32);
       }
+      // all the warp's column tiles with the leading terms first, then with the remainders: an mma never
+      // follows another on the same sums
+      uint32_t bm[NT / 2][4];
 #pragma unroll
-      for (int n2 = 0; n2 < NT / 2; ++n2) {
-        uint32_t bm[4];
-        ldmatrix_x4_trans(bm, v_lane + j * 16 * pitch + n2 * 32);
+      for (int n2 = 0; n2 < NT / 2; ++n2) ldmatrix_x4_trans(bm[n2], v_lane + j * 16 * pitch + n2 * 32);
+#pragma unroll
+      for (int n2 = 0; n2 < NT / 2; ++n2)
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-          mma_bf16(o[mt][2 * n2], hi[mt], bm[0], bm[1]);
-          mma_bf16(o[mt][2 * n2 + 1], hi[mt], bm[2], bm[3]);
-          mma_bf16(o[mt][2 * n2], lo[mt], bm[0], bm[1]);
-          mma_bf16(o[mt][2 * n2 + 1], lo[mt], bm[2], bm[3]);
+          mma_bf16(o[mt][2 * n2], hi[mt], bm[n2][0], bm[n2][1]);
+          mma_bf16(o[mt][2 * n2 + 1], hi[mt], bm[n2][2], bm[n2][3]);
         }
-      }
+#pragma unroll
+      for (int n2 = 0; n2 < NT / 2; ++n2)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_bf16(o[mt][2 * n2], lo[mt], bm[n2][0], bm[n2][1]);
+          mma_bf16(o[mt][2 * n2 + 1], lo[mt], bm[n2][2], bm[n2][3]);
+        }
     }
     __syncthreads();          // everyone is done with this buffer, the weights and the maxima
   }
