@@ -274,10 +274,10 @@ latent_attend_kernel(const T* __restrict__ qk, const T* __restrict__ c_cache, co
 
 // A row's segments joined: the largest of the segments' maxima first (lanes over segments), then
 // every segment's sums weighted by 2^(its maximum - the largest) and added in segment order, then
-// the division. A warp takes 128 elements of a row (blockIdx.y says which), so that the loads of
-// a segment do not wait for the segment before it and few rows still fill the GPU.
-constexpr int MERGE_SLICE = 128;
-
+// the division. A warp takes MERGE_SLICE elements of a row (blockIdx.y says which), so that the loads
+// of a segment do not wait for the segment before it; with few rows a warp takes 32, and the
+// rows still fill the GPU.
+template <int MERGE_SLICE>
 __global__ void __launch_bounds__(WARPS * 32)
 latent_merge_kernel(const float* __restrict__ partial, int segments, float* __restrict__ out,
                     const int* __restrict__ token_list, int tokens, int heads, int rank) {
@@ -319,6 +319,16 @@ latent_merge_kernel(const float* __restrict__ partial, int segments, float* __re
     const int idx = first + lane + 32 * i;
     if (idx < rank) orow[idx] = acc[i] * inv;
   }
+}
+
+void launch_merge(int64_t blocks, cudaStream_t stream, const float* partial, int segments, float* out, const int* token_list,
+                  int tokens, int heads, int rank) {
+  if (blocks * ((rank + 127) / 128) >= 2 * 148)
+    vosti_launch(latent_merge_kernel<128>, dim3((unsigned)blocks, (rank + 127) / 128), dim3(WARPS * 32), 0, stream, partial,
+                 segments, out, token_list, tokens, heads, rank);
+  else
+    vosti_launch(latent_merge_kernel<32>, dim3((unsigned)blocks, (rank + 31) / 32), dim3(WARPS * 32), 0, stream, partial,
+                 segments, out, token_list, tokens, heads, rank);
 }
 
 template <typename T, int RW>
@@ -433,8 +443,7 @@ VOSTI_API int vosti_latent_attend(const void* qk, const void* c_cache, const voi
     if (segments > 1) {                                                                                                 \
       cudaError_t e = cudaGetLastError();                                                                               \
       if (e != cudaSuccess) { vosti_set_error("%s", cudaGetErrorString(e)); return (int)e; }                            \
-      vosti_launch(latent_merge_kernel, dim3((unsigned)blocks, (rank + MERGE_SLICE - 1) / MERGE_SLICE), dim3(WARPS * 32), 0, \
-                   stream, (const float*)partial, segments, out, token_list, tokens, heads, rank);                      \
+      launch_merge(blocks, stream, partial, segments, out, token_list, tokens, heads, rank);                           \
     }                                                                                                                   \
   } while (0)
   if (rw == 4) VOSTI_LA(4);
@@ -454,7 +463,6 @@ VOSTI_API int vosti_latent_merge(const float* partial, int segments, float* out,
   if (tokens == 0) return VOSTI_OK;
   const int64_t blocks = ((int64_t)tokens * heads + WARPS - 1) / WARPS;
   VOSTI_REQUIRE(blocks <= 0x7fffffffLL, "latent_merge: too many (token, head) pairs");
-  const dim3 grid((unsigned)blocks, (rank + MERGE_SLICE - 1) / MERGE_SLICE), block(WARPS * 32);
-  vosti_launch(latent_merge_kernel, grid, block, 0, stream, partial, segments, out, (const int*)nullptr, tokens, heads, rank);
+  launch_merge(blocks, stream, partial, segments, out, nullptr, tokens, heads, rank);
   VOSTI_LAUNCH_CHECK();
 }
