@@ -28,8 +28,8 @@ constexpr int LKT = 64;            // keys of a tile
 constexpr int P_PITCH = LKT * 2 + 16;
 constexpr float LOG2E = 1.4426950408889634f;
 
-template <int RANK, int MT>
-__global__ void __launch_bounds__(LW * 32, 1)
+template <int RANK, int MT, int HALVES>
+__global__ void __launch_bounds__(LW * HALVES * 32, 1)
 latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c_cache, const bf16* __restrict__ r_cache,
                          float* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ cu_q,
                          const int* __restrict__ block_table, int max_pages, int page_size, int num_pages, int heads,
@@ -38,9 +38,11 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
   extern __shared__ __align__(16) uint8_t smem[];
   pdl_wait();
   pdl_launch_dependents();
-  constexpr int ROWS = 16 * MT;
+  constexpr int ROWS = 16 * MT * HALVES;         // HALVES groups of LW warps, each with MT row tiles of its own
+  constexpr int NW = LW * HALVES;
   constexpr int NT = RANK / (8 * LW);            // 8-column tiles of the result a warp owns
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31, warp_all = threadIdx.x >> 5;
+  const int warp = warp_all % LW, half_row = (warp_all / LW) * 16 * MT;     // the group's first row of the tile
   const int b = blockIdx.y;
   const int q_start = cu_q[b], q_len = cu_q[b + 1] - q_start;
   const int rows_total = q_len * heads;
@@ -55,7 +57,7 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
   float* red_s = reinterpret_cast<float*>(p_s + 2 * ROWS * P_PITCH);       // [LW][ROWS]
 
   const int64_t first_row = (int64_t)q_start * heads + row0;                // in [tokens * heads]
-  for (int i = threadIdx.x; i < ROWS * chunks; i += LW * 32) {
+  for (int i = threadIdx.x; i < ROWS * chunks; i += NW * 32) {
     const int r = i / chunks, c = i % chunks;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (row0 + r < rows_total) v = *reinterpret_cast<const uint4*>(qk + (first_row + r) * kw + c * 8);
@@ -68,7 +70,7 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      const int packed = row0 + mt * 16 + (lane >> 2) + 8 * r;
+      const int packed = row0 + half_row + mt * 16 + (lane >> 2) + 8 * r;
       pos_row[mt][r] = packed < rows_total ? positions[q_start + packed / heads] : -1;     // -1: sees nothing, writes nothing
       kstart_row[mt][r] = pos_row[mt][r] >= 0 ? first_visible_key(pos_row[mt][r], window) : 0;
     }
@@ -82,7 +84,7 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
   const int segments = gridDim.z;
   if (first_key >= key_end) {                    // nothing of this segment is visible: empty records
     if (partial != nullptr)
-      for (int r = threadIdx.x; r < ROWS && row0 + r < rows_total; r += LW * 32) {
+      for (int r = threadIdx.x; r < ROWS && row0 + r < rows_total; r += NW * 32) {
         float* rec = partial + ((first_row + r) * segments + blockIdx.z) * (int64_t)(RANK + 2);
         rec[0] = -INFINITY;
         rec[1] = 0.f;
@@ -99,8 +101,8 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
     uint8_t* dst = k_s + buffer * (LKT * pitch);
     // lane i looks up the slot of the warp's i-th row; the rows then take it from there
     int64_t my_slot = -1;
-    if (lane < LKT / LW) {
-      const int key = key0 + warp + lane * LW;
+    if (lane < LKT / NW) {
+      const int key = key0 + warp_all + lane * NW;
       if (key >= first_key && key < key_end) {
         const int index = key / page_size;
         const int page = index < max_pages ? table[index] : -1;
@@ -109,8 +111,8 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
       }
     }
 #pragma unroll
-    for (int i = 0; i < LKT / LW; ++i) {
-      const int r = warp + i * LW;
+    for (int i = 0; i < LKT / NW; ++i) {
+      const int r = warp_all + i * NW;
       int64_t slot = __shfl_sync(0xffffffffu, my_slot, i);
       const bool valid = slot >= 0;
       if (!valid) slot = 0;
@@ -157,7 +159,7 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[mt][e] = sa[mt][e] = sb[mt][e] = sc[mt][e] = 0.f;
     const uint32_t k_lane = smem_addr(ks + (warp * 8 + (lane & 7)) * pitch + (lane >> 3) * 16);
-    const uint32_t q_lane = smem_addr(q_s + (lane & 15) * pitch + (lane >> 4) * 16);
+    const uint32_t q_lane = smem_addr(q_s + (half_row + (lane & 15)) * pitch + (lane >> 4) * 16);
     auto step = [&](int kk, float (&first)[MT][4], float (&second)[MT][4]) {       // 32 elements of the key: two mma k-steps
       uint32_t bm[4];
       ldmatrix_x4(bm, k_lane + kk * 64);
@@ -197,7 +199,7 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
       for (int r = 0; r < 2; ++r) {
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-        if ((lane & 3) == 0) red_s[warp * ROWS + mt * 16 + (lane >> 2) + 8 * r] = tile_max[r];
+        if ((lane & 3) == 0) red_s[warp * ROWS + half_row + mt * 16 + (lane >> 2) + 8 * r] = tile_max[r];
       }
     }
     __syncthreads();
@@ -206,7 +208,7 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
       float alpha[2];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        const int row = mt * 16 + (lane >> 2) + 8 * r;
+        const int row = half_row + mt * 16 + (lane >> 2) + 8 * r;
         float tile_max = -INFINITY;
 #pragma unroll
         for (int w = 0; w < LW; ++w) tile_max = fmaxf(tile_max, red_s[w * ROWS + row]);
@@ -231,7 +233,7 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
     }
     __syncthreads();
     // ---- O += (P_hi + P_lo) C over the warp's columns, 16 keys at a time
-    const uint32_t p_lane = smem_addr(p_s + (lane & 15) * P_PITCH + (lane >> 4) * 16);
+    const uint32_t p_lane = smem_addr(p_s + (half_row + (lane & 15)) * P_PITCH + (lane >> 4) * 16);
     const uint32_t v_lane = smem_addr(ks + ((lane & 7) + ((lane >> 3) & 1) * 8) * pitch + (col0 + (lane >> 4) * 8) * 2);
 #pragma unroll
     for (int j = 0; j < LKT / 16; ++j) {
@@ -273,7 +275,7 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
       float l = l_row[mt][r];
       l += __shfl_xor_sync(0xffffffffu, l, 1);
       l += __shfl_xor_sync(0xffffffffu, l, 2);
-      if ((lane & 3) == 0) red_s[warp * ROWS + mt * 16 + (lane >> 2) + 8 * r] = l;
+      if ((lane & 3) == 0) red_s[warp * ROWS + half_row + mt * 16 + (lane >> 2) + 8 * r] = l;
     }
   __syncthreads();
 #pragma unroll
@@ -281,7 +283,7 @@ latent_attend_mma_kernel(const bf16* __restrict__ qk, const bf16* __restrict__ c
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       if (pos_row[mt][r] < 0) continue;
-      const int row = mt * 16 + (lane >> 2) + 8 * r;
+      const int row = half_row + mt * 16 + (lane >> 2) + 8 * r;
       float l = 0.f;
 #pragma unroll
       for (int w = 0; w < LW; ++w) l += red_s[w * ROWS + row];
@@ -451,16 +453,16 @@ head_project_mma_kernel(const void* __restrict__ x_, int64_t x_row, int64_t x_he
   }
 }
 
-size_t latent_mma_smem(int rank, int rot, int mt) {
+size_t latent_mma_smem(int rank, int rot, int rows) {
   const size_t pitch = (size_t)(rank + rot) * 2 + 16;
-  return (16 * mt + 2 * LKT) * pitch + 2 * 16 * mt * P_PITCH + LW * 16 * mt * sizeof(float);
+  return (rows + 2 * LKT) * pitch + 2 * rows * P_PITCH + LW * rows * sizeof(float);
 }
 
 }  // namespace
 
 // 1 if the tensor-core kernel takes these sizes (bfloat16 is the caller's to check).
 VOSTI_API int vosti_latent_attend_mma_fits(int rank, int rot) {
-  return (rank == 128 || rank == 256 || rank == 512) && rot > 0 && rot % 32 == 0 && latent_mma_smem(rank, rot, 2) <= 227 * 1024;
+  return (rank == 128 || rank == 256 || rank == 512) && rot > 0 && rot % 32 == 0 && latent_mma_smem(rank, rot, 32) <= 227 * 1024;
 }
 
 // qk bf16 [tokens, heads, rank + rot]; caches bf16 [pages, 1, page_size, rank | rot]; out float32
@@ -479,26 +481,27 @@ VOSTI_API int vosti_latent_attend_mma(const void* qk, const void* c_cache, const
                 "latent_attend_mma: key segments need scratch and a length that is a multiple of %d", LKT);
   if (requests == 0 || max_q_len == 0) return VOSTI_OK;
   const int64_t most_rows = (int64_t)max_q_len * heads;
-  const int mt = most_rows > 16 ? 2 : 1;
-  const int64_t tiles = (most_rows + 16 * mt - 1) / (16 * mt);
+  const int halves = most_rows > 16 ? 2 : 1;      // 32 rows: two groups of warps with a row tile each over the same keys
+  const int rows = 16 * halves;
+  const int64_t tiles = (most_rows + rows - 1) / rows;
   VOSTI_REQUIRE(tiles <= 0x7fffffffLL, "latent_attend_mma: too many rows");
   const dim3 grid((unsigned)tiles, requests, segments);
-  const size_t smem = latent_mma_smem(rank, rot, mt);
+  const size_t smem = latent_mma_smem(rank, rot, rows);
   float* partial = segments > 1 ? scratch : nullptr;
-#define VOSTI_LM(RANK, MT)                                                                                              \
+#define VOSTI_LM(RANK, HALVES)                                                                                          \
   do {                                                                                                                  \
     static bool configured = false;                                                                                     \
     if (!configured) {                                                                                                  \
-      cudaFuncSetAttribute(latent_attend_mma_kernel<RANK, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); \
+      cudaFuncSetAttribute(latent_attend_mma_kernel<RANK, 1, HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); \
       configured = true;                                                                                                \
     }                                                                                                                   \
-    vosti_launch(latent_attend_mma_kernel<RANK, MT>, grid, dim3(LW * 32), smem, stream, (const bf16*)qk,                \
+    vosti_launch(latent_attend_mma_kernel<RANK, 1, HALVES>, grid, dim3(LW * HALVES * 32), smem, stream, (const bf16*)qk, \
                  (const bf16*)c_cache, (const bf16*)r_cache, out, positions, cu_q, block_table, max_pages, page_size,   \
                  num_pages, heads, rot, scale * LOG2E, window, partial, segment, status);                               \
   } while (0)
-  if (rank == 512) { if (mt == 2) VOSTI_LM(512, 2); else VOSTI_LM(512, 1); }
-  else if (rank == 256) { if (mt == 2) VOSTI_LM(256, 2); else VOSTI_LM(256, 1); }
-  else { if (mt == 2) VOSTI_LM(128, 2); else VOSTI_LM(128, 1); }
+  if (rank == 512) { if (halves == 2) VOSTI_LM(512, 2); else VOSTI_LM(512, 1); }
+  else if (rank == 256) { if (halves == 2) VOSTI_LM(256, 2); else VOSTI_LM(256, 1); }
+  else { if (halves == 2) VOSTI_LM(128, 2); else VOSTI_LM(128, 1); }
 #undef VOSTI_LM
   VOSTI_LAUNCH_CHECK();
 }
