@@ -25,8 +25,10 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
 // A thread takes one channel (neighbouring threads neighbouring channels) and `per_block` tokens one
-// after the other, so that the taps' weights and the inputs a token shares with the one before it
-// come from the first-level cache.
+// after the other. With up to 8 taps the taps' weights and the last inputs stay in registers: a token
+// costs one load; the window is filled anew at the block's first token and where a request starts.
+constexpr int CONV_WINDOW = 8;
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 scan_conv_kernel(const T* __restrict__ xz, int64_t xz_stride, const void* __restrict__ conv_w, const void* __restrict__ conv_b,
@@ -36,25 +38,68 @@ scan_conv_kernel(const T* __restrict__ xz, int64_t xz_stride, const void* __rest
   pdl_wait();
   pdl_launch_dependents();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  const int t_end = min(tokens, ((int)blockIdx.y + 1) * per_block);
-  for (int t = blockIdx.y * per_block; t < t_end; ++t) {
-    const int b = request_of[t];
-    const int first = cu_q[b], slot = state_slots[b];
-    if (slot < 0 || slot >= num_slots) {
-      if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
-      continue;
+  const int t_begin = blockIdx.y * per_block, t_end = min(tokens, t_begin + per_block);
+  const bool live = c < inner;
+  const float bias = live && conv_b != nullptr ? load_flex(conv_b, w_f32, c) : 0.f;
+  // the input `ago` tokens before token t of request b (portion starting at `first`, state in `tail`)
+  auto input = [&](int t, int ago, int first, const float* tail) {
+    const int back = t - first;
+    return ago <= back ? to_f32(xz[(int64_t)(t - ago) * xz_stride + c])
+                       : tail[(int64_t)(taps - 1 - (ago - back)) * inner + c];           // the tail's last row is the newest
+  };
+  int b = -1, first = 0, next_first = 0;
+  const float* tail = nullptr;
+  bool usable = false;
+  if (taps <= CONV_WINDOW) {
+    float w[CONV_WINDOW], win[CONV_WINDOW];          // right-aligned: index CONV_WINDOW - 1 - k is k tokens ago
+#pragma unroll
+    for (int k = 0; k < CONV_WINDOW; ++k) {
+      w[CONV_WINDOW - 1 - k] = live && k < taps ? load_flex(conv_w, w_f32, (int64_t)c * taps + taps - 1 - k) : 0.f;
+      win[k] = 0.f;
     }
-    if (c >= inner) continue;
-    const float* tail = state + (int64_t)slot * state_stride + tail_offset;          // [taps - 1, inner]
-    const int back = t - first;                                                       // tokens of the portion before this one
-    float acc = conv_b != nullptr ? load_flex(conv_b, w_f32, c) : 0.f;
-    for (int j = 0; j < taps; ++j) {
-      const int ago = taps - 1 - j;                                                   // tap j reads the input `ago` tokens back
-      float u;
-      if (ago <= back) u = to_f32(xz[(int64_t)(t - ago) * xz_stride + c]);
-      else u = tail[(int64_t)(taps - 1 - (ago - back)) * inner + c];                  // the tail's last row is the newest
-      acc = fmaf(load_flex(conv_w, w_f32, (int64_t)c * taps + j), u, acc);
+    for (int t = t_begin; t < t_end; ++t) {
+      const bool fresh = b < 0 || t >= next_first;
+      if (fresh) {
+        b = request_of[t];
+        first = cu_q[b];
+        next_first = cu_q[b + 1];
+        const int slot = state_slots[b];
+        usable = slot >= 0 && slot < num_slots;
+        if (!usable && threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
+        tail = state + (int64_t)(usable ? slot : 0) * state_stride + tail_offset;        // [taps - 1, inner]
+      }
+      if (!usable || !live) continue;
+      if (fresh) {
+#pragma unroll
+        for (int k = 1; k < CONV_WINDOW; ++k) win[CONV_WINDOW - 1 - k] = k < taps ? input(t, k, first, tail) : 0.f;
+      } else {
+#pragma unroll
+        for (int k = CONV_WINDOW - 1; k >= 1; --k) win[CONV_WINDOW - 1 - k] = win[CONV_WINDOW - k];
+      }
+      win[CONV_WINDOW - 1] = to_f32(xz[(int64_t)t * xz_stride + c]);
+      // oldest tap first, as in the loop over the taps below
+      float acc = bias;
+#pragma unroll
+      for (int k = CONV_WINDOW - 1; k >= 0; --k)
+        if (k < taps) acc = fmaf(w[CONV_WINDOW - 1 - k], win[CONV_WINDOW - 1 - k], acc);
+      out[(int64_t)t * inner + c] = from_f32<T>(silu_f(acc));
     }
+    return;
+  }
+  for (int t = t_begin; t < t_end; ++t) {
+    if (b < 0 || t >= next_first) {
+      b = request_of[t];
+      first = cu_q[b];
+      next_first = cu_q[b + 1];
+      const int slot = state_slots[b];
+      usable = slot >= 0 && slot < num_slots;
+      if (!usable && threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
+      tail = state + (int64_t)(usable ? slot : 0) * state_stride + tail_offset;
+    }
+    if (!usable || !live) continue;
+    float acc = bias;
+    for (int j = 0; j < taps; ++j)                                                      // tap j reads the input taps - 1 - j tokens back
+      acc = fmaf(load_flex(conv_w, w_f32, (int64_t)c * taps + j), input(t, taps - 1 - j, first, tail), acc);
     out[(int64_t)t * inner + c] = from_f32<T>(silu_f(acc));
   }
 }
