@@ -588,7 +588,7 @@ def close_rows(got, want, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_whole_prompt_portions_and_decoding_against_plain(models, name, dtype):
     folder, config, W = models[name]
     tokens = prompt(config, 77, 1)                              # past every window of every layer
@@ -647,7 +647,8 @@ def test_residual_stream_after_every_layer(models):
             assert torch.allclose(got, expected.float(), atol=3e-4, rtol=3e-4), (name, i)
 
 
-@pytest.mark.parametrize("name,dtype", [("a", "float32"), ("b", "float32"), ("c", "float32"), ("c", "bfloat16"), ("a", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("a", "float32"), ("b", "float32"), ("c", "float32"), ("c", "bfloat16"), ("a", "bfloat16"),
+                                        ("d", "float32"), ("d", "bfloat16")])
 def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(models, name, dtype):
     """Four requests through two state slots and a pool that holds two of them: portions of some
     beside single tokens of others; every request equals itself alone."""

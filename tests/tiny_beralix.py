@@ -15,6 +15,9 @@ B: values of one: one head, one state, a step-size rank of one, a convolution of
 C: attention heads of 64 with equal key and value widths and pages of 16 tokens (the sizes the
    tensor-core attention kernels take in bfloat16), latent widths in whole 16-byte words, 40
    states (eight lanes a channel), two scan layers in a row.
+D: latent layers of the sizes the tensor-core latent kernels take in bfloat16 (latents of 128 and
+   256, rotated parts of 32 and 64), one whose projection rows are whole 16-byte words (its
+   per-head products run on the tensor cores both ways) and one whose are not; 12 states.
 """
 import json
 from pathlib import Path
@@ -73,8 +76,15 @@ C = dict(architecture="Beralix", vocab=160, width=128, norm=dict(eps=1e-6), logi
     _scan(64, 16, 2, 16, None),
     _window(2, 2, 64, 64, 0.5, 33, 50000.0, 64, None, True, _dense(128)),
 ])
-ALL = {"a": (A, 31), "b": (B, 32), "c": (C, 33)}      # config, seed
-PAGE = {"a": 8, "b": 4, "c": 16}
+D = dict(architecture="Beralix", vocab=192, width=96, norm=dict(eps=1e-5), logit_softcap=15.0, layers=[
+    _latent(8, 24, 32, 40, 128, 0.5, 8000.0, _scaling(4.0, 64, 8.0, 1.0), _dense(96)),
+    _scan(128, 12, 3, 6, _dense(48)),
+    _window(4, 1, 64, 64, 0.4, 19, 100000.0, 32, None, True, None),
+    _latent(4, 32, 64, 16, 256, 0.45, 1000.0, None, _dense(64)),
+    _window(4, 1, 64, 64, 0.4, 50, 100000.0, 64, _scaling(2.0, 32, 4.0, 1.0), True, _dense(96)),
+])
+ALL = {"a": (A, 31), "b": (B, 32), "c": (C, 33), "d": (D, 34)}      # config, seed
+PAGE = {"a": 8, "b": 4, "c": 16, "d": 16}
 
 
 def draw(name, shape, gen):
