@@ -298,19 +298,29 @@ latent_merge_kernel(const float* __restrict__ partial, int segments, float* __re
 #pragma unroll
   for (int i = 0; i < MERGE_SLICE / 32; ++i) acc[i] = 0.f;
   if (top != -INFINITY) {
-#pragma unroll 4
-    for (int s = 0; s < segments; ++s) {
-      const float* rec = row + (int64_t)s * (rank + 2);
-      const float ms = rec[0];
-      if (ms == -INFINITY) continue;                  // a segment without a visible key left no sums
-      const float c = exp2f(ms - top);
-      l = fmaf(rec[1], c, l);
+    // 32 segments at a time: lane j reads segment j's maximum and sum, so that the loop over the
+    // segments' sums waits for no scalar; the sums are added in segment order
+    for (int base = 0; base < segments; base += 32) {
+      const int mine = base + lane;
+      const float ms = mine < segments ? row[(int64_t)mine * (rank + 2)] : -INFINITY;
+      const float ls = mine < segments ? row[(int64_t)mine * (rank + 2) + 1] : 0.f;     // every record has its sum of weights
+      const float weight = ms == -INFINITY ? 0.f : exp2f(ms - top);     // a segment without a visible key left no sums
+      if (weight != 0.f) l = fmaf(ls, weight, l);
+      const int count = min(32, segments - base);
+#pragma unroll 8
+      for (int j = 0; j < count; ++j) {
+        const float c = __shfl_sync(0xffffffffu, weight, j);
+        const float* rec = row + (int64_t)(base + j) * (rank + 2);
 #pragma unroll
-      for (int i = 0; i < MERGE_SLICE / 32; ++i) {
-        const int idx = first + lane + 32 * i;
-        if (idx < rank) acc[i] = fmaf(rec[2 + idx], c, acc[i]);
+        for (int i = 0; i < MERGE_SLICE / 32; ++i) {
+          const int idx = first + lane + 32 * i;
+          const float v = (c != 0.f && idx < rank) ? rec[2 + idx] : 0.f;
+          acc[i] = fmaf(v, c, acc[i]);
+        }
       }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
   float* orow = out + ((int64_t)t * heads + h) * rank;
