@@ -710,6 +710,30 @@ def test_long_decoding_past_every_window(models, name):
     assert close_rows(torch.cat(rows), want, "float32")
 
 
+@pytest.mark.parametrize("name,dtype,binary", [("a", "float32", True), ("d", "bfloat16", False), ("c", "float32", False)])
+def test_trace_replay_of_a_mixed_schedule(models, name, dtype, binary, tmp_path):
+    """The trace runner (the program itself, and the class it wraps) over a schedule of up to four
+    live requests, portions beside single tokens, requests that sit a step out, a pool smaller
+    than the sum of all requests and four state slots for six requests: every row against the
+    plain implementation of the request alone."""
+    import numpy as np
+    import replay_util as R
+    folder, config, W = models[name]
+    requests = {f"q{i}": prompt(config, n, 60 + i) for i, n in enumerate([70, 40, 33, 90, 64, 21])}
+    steps = R.number(R.mixed_steps(requests, seed=5))
+    max_tokens = R.max_live_tokens(steps)
+    assert max_tokens < sum(R.roundup64(len(t)) for t in requests.values())
+    if binary:
+        R.run_binary(folder, dtype, steps, max_tokens, tmp_path)
+    else:
+        R.run_in_process(folder, dtype, steps, max_tokens, tiny.PAGE[name], tmp_path)
+    rows = R.collect(steps, tmp_path, config["vocab"])
+    assert len(rows) == sum(len(t) for t in requests.values())
+    for rid, tokens in requests.items():
+        got = torch.from_numpy(np.stack([rows[(rid, p)] for p in range(len(tokens))]))
+        assert close_rows(got, logits_of(config, W, tokens), dtype), rid
+
+
 def plain_greedy(config, W, tokens, new_tokens):
     tokens, out = list(tokens), []
     for _ in range(new_tokens):
