@@ -71,7 +71,7 @@ B = dict(architecture="Beralix", vocab=128, width=64, norm=dict(eps=1e-5), logit
 ])
 C = dict(architecture="Beralix", vocab=160, width=128, norm=dict(eps=1e-6), logit_softcap=25.0, layers=[
     _window(4, 2, 64, 64, 0.5, 48, 10000.0, 32, _scaling(8.0, 64, 8.0, 1.0), True, _dense(192)),
-    _latent(4, 32, 16, 48, 64, 0.6, 20000.0, _scaling(4.0, 128, 16.0, 1.0), _dense(64)),
+    _latent(4, 40, 16, 56, 64, 0.6, 20000.0, _scaling(4.0, 128, 16.0, 1.0), _dense(64)),
     _scan(96, 40, 3, 8, _dense(64)),
     _scan(64, 16, 2, 16, None),
     _window(2, 2, 64, 64, 0.5, 33, 50000.0, 64, None, True, _dense(128)),
@@ -79,9 +79,9 @@ C = dict(architecture="Beralix", vocab=160, width=128, norm=dict(eps=1e-6), logi
 D = dict(architecture="Beralix", vocab=192, width=96, norm=dict(eps=1e-5), logit_softcap=15.0, layers=[
     _latent(8, 24, 32, 40, 128, 0.5, 8000.0, _scaling(4.0, 64, 8.0, 1.0), _dense(96)),
     _scan(128, 12, 3, 6, _dense(48)),
-    _window(4, 1, 64, 64, 0.4, 19, 100000.0, 32, None, True, None),
+    _window(8, 2, 64, 64, 0.4, 19, 100000.0, 32, None, True, None),
     _latent(4, 32, 64, 16, 256, 0.45, 1000.0, None, _dense(64)),
-    _window(4, 1, 64, 64, 0.4, 50, 100000.0, 64, _scaling(2.0, 32, 4.0, 1.0), True, _dense(96)),
+    _window(8, 2, 64, 64, 0.4, 50, 100000.0, 64, _scaling(2.0, 32, 4.0, 1.0), True, _dense(96)),
 ])
 ALL = {"a": (A, 31), "b": (B, 32), "c": (C, 33), "d": (D, 34)}      # config, seed
 PAGE = {"a": 8, "b": 4, "c": 16, "d": 16}
