@@ -6,11 +6,13 @@ from .qwen3 import Qwen3Config
 from . import mugizen as _mugizen
 from . import vivesun as _vivesun
 from . import beralix as _beralix
+from . import nefipel as _nefipel
 
 register_architecture(_qwen3.ARCHITECTURE, _qwen3.spec_from_config, replace=True)
 register_architecture(_mugizen.ARCHITECTURE, _mugizen.spec_from_config, replace=True)
 register_architecture(_vivesun.ARCHITECTURE, _vivesun.spec_from_config, replace=True)
 register_architecture(_beralix.ARCHITECTURE, _beralix.spec_from_config, replace=True)
+register_architecture(_nefipel.ARCHITECTURE, _nefipel.spec_from_config, replace=True)
 
 __all__ = [
     "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config",

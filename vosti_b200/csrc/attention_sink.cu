@@ -182,7 +182,185 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
   }
 }
 
+// What may follow a head's attention before the output projection, in float32:
+//   * with two score maps a head (differential attention): o = a1 - lambda * a2, a1 and a2 the two
+//     maps' softmax-weighted sums of the same values;
+//   * `unit_norm`: o / sqrt(mean(o^2) + eps) over the head's values (no weight), times `out_scale`;
+//   * `gate`: o * sigmoid(gate[t, h * dv + i]), the gate a product of the same input (float32 or
+//     bfloat16 rows `gate_stride` elements apart).
+struct HeadFinish {
+  float lambda;
+  float out_scale;
+  float eps;
+  int unit_norm;
+  const void* gate;
+  int gate_f32;
+  long long gate_stride;
+};
+
+// acc[m][i]: map m's unnormalised sum for value element lane + 32 i; inv[m] = 1 / its denominator. One warp.
+template <typename T, int MAPS>
+__device__ __forceinline__ void finish_head(const float (&acc)[MAPS][MAX_W / 32], const float (&inv)[MAPS], const HeadFinish& f,
+                                            int t, int h, int dv, T* __restrict__ orow) {
+  const int lane = threadIdx.x & 31;
+  float o[MAX_W / 32];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAX_W / 32; ++i) {
+    o[i] = acc[0][i] * inv[0];
+    if (MAPS == 2) o[i] -= f.lambda * (acc[MAPS - 1][i] * inv[MAPS - 1]);
+    if (lane + 32 * i < dv) ss += o[i] * o[i];
+  }
+  float by = 1.f;
+  if (f.unit_norm) by = f.out_scale / sqrtf(warp_sum(ss) / (float)dv + f.eps);
+#pragma unroll
+  for (int i = 0; i < MAX_W / 32; ++i) {
+    const int idx = lane + 32 * i;
+    if (idx < dv) {
+      float y = f.unit_norm ? o[i] * by : o[i];
+      if (f.gate != nullptr) y *= 1.f / (1.f + expf(-load_flex(f.gate, f.gate_f32, (int64_t)t * f.gate_stride + (int64_t)h * dv + idx)));
+      orow[idx] = from_f32<T>(y);
+    }
+  }
+}
+
+// The same on attention outputs another kernel wrote: a [tokens, nq, MAPS, dv] -> out [tokens, nq, dv].
+template <typename T, int MAPS>
+__global__ void __launch_bounds__(WARPS * 32)
+head_finish_kernel(const T* __restrict__ a, T* __restrict__ out, int tokens, int nq, int dv, HeadFinish f) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t wid = (int64_t)blockIdx.x * WARPS + warp;
+  if (wid >= (int64_t)tokens * nq) return;
+  float acc[MAPS][MAX_W / 32], inv[MAPS];
+#pragma unroll
+  for (int m = 0; m < MAPS; ++m) {
+    inv[m] = 1.f;
+#pragma unroll
+    for (int i = 0; i < MAX_W / 32; ++i) {
+      const int idx = lane + 32 * i;
+      acc[m][i] = idx < dv ? to_f32(a[(wid * MAPS + m) * dv + idx]) : 0.f;
+    }
+  }
+  finish_head<T, MAPS>(acc, inv, f, (int)(wid / nq), (int)(wid % nq), dv, out + wid * dv);
+}
+
+// After a q | k | v projection (float32 or the serving type, rows `proj_stride` elements apart so that
+// further columns may follow), one block per token and a warp per head: add the projection's bias;
+// RMS-norm every query and key head over its dk elements with a weight shared by all heads; turn the
+// first 2 * rot_half elements of the head by position * freq[i], element i with i + rot_half or, with
+// `interleaved`, 2i with 2i + 1 (cos and sin times `magnitude`); queries go to q_out
+// [tokens, nq * maps * dk], keys and values to their cache slots. With `maps` score maps a head the
+// projection holds nq * maps query heads and nkv * maps key heads, head by head, and the key cache's
+// entry of a kv head is its maps keys side by side: [pages, nkv, page_size, maps * dk].
 template <typename T>
+__global__ void __launch_bounds__(256)
+qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_stride, const float* __restrict__ bias,
+                 T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ positions,
+                 const int* __restrict__ slot_mapping, int64_t num_slots, int page_size, int nq, int nkv, int maps, int dk, int dv,
+                 const void* __restrict__ q_norm, const void* __restrict__ k_norm, int norm_f32, float eps,
+                 const float* __restrict__ freq, int rot_half, int interleaved, float magnitude, unsigned* status) {
+  extern __shared__ float heads_smem[];          // [2 * rot_half] cosines and sines, then [warps][dk] a head per warp
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float* turn = heads_smem;
+  float* buf = heads_smem + 2 * rot_half + warp * dk;
+  if (rot_half > 0) {
+    const float p = (float)positions[t];
+    for (int i = threadIdx.x; i < rot_half; i += blockDim.x) {
+      const float angle = p * freq[i];
+      turn[i] = cosf(angle) * magnitude;
+      turn[rot_half + i] = sinf(angle) * magnitude;
+    }
+    __syncthreads();
+  }
+  int64_t page = 0, offset = 0;
+  bool store = k_cache != nullptr;
+  if (store) {
+    const int64_t slot = slot_mapping[t];
+    if (slot < 0 || slot >= num_slots) {
+      if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
+      store = false;
+    }
+    page = slot / page_size;
+    offset = slot % page_size;
+  }
+  const int nqm = nq * maps, nkm = nkv * maps;
+  const int64_t wq = (int64_t)nqm * dk, wk = (int64_t)nkm * dk;
+  const int64_t row = (int64_t)t * proj_stride;
+  for (int hd = warp; hd < nqm + nkm + nkv; hd += nwarps) {
+    if (hd >= nqm + nkm) {                         // a value head: bias, then its cache slot
+      if (!store) continue;
+      const int g = hd - nqm - nkm;
+      const int64_t off = wq + wk + (int64_t)g * dv;
+      T* dst = v_cache + ((page * nkv + g) * page_size + offset) * dv;
+      for (int i = lane; i < dv; i += 32) {
+        float x = load_flex(proj, proj_f32, row + off + i);
+        if (bias != nullptr) x += bias[off + i];
+        dst[i] = from_f32<T>(x);
+      }
+      continue;
+    }
+    const bool is_q = hd < nqm;
+    if (!is_q && !store) continue;
+    const int64_t off = (int64_t)hd * dk;          // query heads, then key heads, in the projection's order
+    const void* norm_w = is_q ? q_norm : k_norm;
+    float x[MAX_W / 32];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAX_W / 32; ++j) {
+      const int i = lane + 32 * j;
+      x[j] = 0.f;
+      if (i < dk) {
+        x[j] = load_flex(proj, proj_f32, row + off + i);
+        if (bias != nullptr) x[j] += bias[off + i];
+        ss += x[j] * x[j];
+      }
+    }
+    if (norm_w != nullptr) {
+      const float inv = 1.f / sqrtf(warp_sum(ss) / (float)dk + eps);
+#pragma unroll
+      for (int j = 0; j < MAX_W / 32; ++j) {
+        const int i = lane + 32 * j;
+        if (i < dk) x[j] = x[j] * inv * load_flex(norm_w, norm_f32, i);
+      }
+    }
+    T* dst;
+    if (is_q) {
+      dst = q_out + (int64_t)t * wq + off;
+    } else {
+      const int kh = hd - nqm, g = kh / maps, m = kh % maps;
+      dst = k_cache + (((page * nkv + g) * page_size + offset) * maps + m) * dk;
+    }
+    if (rot_half > 0) {
+#pragma unroll
+      for (int j = 0; j < MAX_W / 32; ++j)
+        if (lane + 32 * j < dk) buf[lane + 32 * j] = x[j];
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < MAX_W / 32; ++j) {
+        const int i = lane + 32 * j;
+        if (i < 2 * rot_half) {
+          const bool first = interleaved ? (i & 1) == 0 : i < rot_half;
+          const int pair = interleaved ? i >> 1 : (first ? i : i - rot_half);
+          const float other = buf[interleaved ? i ^ 1 : (first ? i + rot_half : i - rot_half)];
+          const float c = turn[pair], sn = turn[rot_half + pair];
+          x[j] = first ? x[j] * c - other * sn : x[j] * c + other * sn;
+        }
+      }
+      __syncwarp();
+    }
+#pragma unroll
+    for (int j = 0; j < MAX_W / 32; ++j) {
+      const int i = lane + 32 * j;
+      if (i < dk) dst[i] = from_f32<T>(x[j]);
+    }
+  }
+}
+
+template <typename T, int MAPS>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                       T* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ request_of,
@@ -190,7 +368,9 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
                       const int* __restrict__ token_list, int tokens,
                       int nq, int nkv, int dk, int dv, float scale_log2, int window, const float* __restrict__ bias,
                       int bias_last, const float* __restrict__ sink, float* __restrict__ partial, int segment,
-                      unsigned* status) {
+                      unsigned* status, HeadFinish finish) {
+  // MAPS score maps a head: the query row holds MAPS queries, a key entry MAPS keys side by side,
+  // every map has a softmax of its own over the same values (a value row is loaded once for all).
   extern __shared__ float q_smem[];
   pdl_wait();
   pdl_launch_dependents();
@@ -199,9 +379,9 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
   if (wid >= (int64_t)tokens * nq) return;
   const int t = token_list != nullptr ? token_list[wid / nq] : (int)(wid / nq), h = (int)(wid % nq);
   const int g = h / (nq / nkv);
-  float* qs = q_smem + warp * dk;
-  const T* qrow = q + ((int64_t)t * nq + h) * dk;
-  for (int i = lane; i < dk; i += 32) qs[i] = to_f32(qrow[i]);
+  float* qs = q_smem + warp * MAPS * dk;
+  const T* qrow = q + ((int64_t)t * nq + h) * MAPS * dk;
+  for (int i = lane; i < MAPS * dk; i += 32) qs[i] = to_f32(qrow[i]);
   __syncwarp();
 
   const int b = request_of[t];
@@ -215,16 +395,23 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
   const int* table = block_table + (int64_t)b * max_pages;
   const float* bias_h = bias != nullptr ? bias + (int64_t)h * (bias_last + 1) : nullptr;
 
-  float m = -INFINITY, l = 0.f;
-  float acc[MAX_W / 32];
+  float m[MAPS], l[MAPS];
+  float acc[MAPS][MAX_W / 32];
 #pragma unroll
-  for (int i = 0; i < MAX_W / 32; ++i) acc[i] = 0.f;
+  for (int a = 0; a < MAPS; ++a) {
+    m[a] = -INFINITY;
+    l[a] = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_W / 32; ++i) acc[a][i] = 0.f;
+  }
 
   for (int j0 = (kstart / 32) * 32; j0 <= kend; j0 += 32) {
     const int j = j0 + lane;
     bool valid = j >= kstart && j <= kend;
     int64_t slot = 0;
-    float s = -INFINITY;
+    float s[MAPS];
+#pragma unroll
+    for (int a = 0; a < MAPS; ++a) s[a] = -INFINITY;
     if (valid) {
       const int slot_in_table = j / page_size;
       const int page = slot_in_table < max_pages ? table[slot_in_table] : -1;
@@ -233,27 +420,40 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
         valid = false;
       } else {
         slot = ((int64_t)page * nkv + g) * page_size + (j % page_size);   // row of (page, head, offset)
-        s = dot_key(qs, k_cache + slot * dk, dk) * scale_log2;
-        if (bias_h != nullptr) s += bias_h[min(pos - j, bias_last)];
+#pragma unroll
+        for (int a = 0; a < MAPS; ++a) {
+          s[a] = dot_key(qs + a * dk, k_cache + (slot * MAPS + a) * dk, dk) * scale_log2;
+          if (bias_h != nullptr) s[a] += bias_h[min(pos - j, bias_last)];
+        }
       }
     }
-    const float tile_max = warp_max(s);
-    if (tile_max == -INFINITY) continue;  // nothing visible here: state untouched
-    const float m_new = fmaxf(m, tile_max);
-    const float alpha = exp2f(m - m_new);
-    const float p = valid ? exp2f(s - m_new) : 0.f;
-    l = l * alpha + warp_sum(p);
+    float p[MAPS];
+    bool any = false;
 #pragma unroll
-    for (int i = 0; i < MAX_W / 32; ++i) acc[i] *= alpha;
+    for (int a = 0; a < MAPS; ++a) {
+      const float tile_max = warp_max(s[a]);
+      p[a] = 0.f;
+      if (tile_max == -INFINITY) continue;  // nothing visible here: state untouched
+      any = true;
+      const float m_new = fmaxf(m[a], tile_max);
+      const float alpha = exp2f(m[a] - m_new);
+      p[a] = valid ? exp2f(s[a] - m_new) : 0.f;
+      l[a] = l[a] * alpha + warp_sum(p[a]);
+#pragma unroll
+      for (int i = 0; i < MAX_W / 32; ++i) acc[a][i] *= alpha;
+      m[a] = m_new;
+    }
+    if (!any) continue;
     const int last = min(31, kend - j0);
     // four keys at a time, so that their value rows are in flight together (keys past the
     // end have p = 0 and slot 0, a row that exists)
     for (int kk = 0; kk <= last; kk += 4) {
-      float pk[4];
+      float pk[MAPS][4];
       const T* vrow[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        pk[u] = __shfl_sync(0xffffffffu, p, kk + u);
+#pragma unroll
+        for (int a = 0; a < MAPS; ++a) pk[a][u] = __shfl_sync(0xffffffffu, p[a], kk + u);
         vrow[u] = v_cache + __shfl_sync(0xffffffffu, slot, kk + u) * dv;
       }
 #pragma unroll
@@ -264,88 +464,90 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
 #pragma unroll
           for (int u = 0; u < 4; ++u) x[u] = to_f32(vrow[u][idx]);
 #pragma unroll
-          for (int u = 0; u < 4; ++u) acc[i] = fmaf(pk[u], x[u], acc[i]);
+          for (int a = 0; a < MAPS; ++a)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[a][i] = fmaf(pk[a][u], x[u], acc[a][i]);
         }
       }
     }
-    m = m_new;
   }
   if (partial != nullptr) {
-    // one record per (row, segment): maximum, sum, then the unnormalised values
-    float* rec = partial + (wid * gridDim.y + blockIdx.y) * (int64_t)(dv + 2);
-    if (lane == 0) {
-      rec[0] = m;
-      rec[1] = l;
-    }
+    // one record per (row, segment, map): maximum, sum, then the unnormalised values
+    float* rec = partial + (wid * gridDim.y + blockIdx.y) * (int64_t)(MAPS * (dv + 2));
 #pragma unroll
-    for (int i = 0; i < MAX_W / 32; ++i) {
-      const int idx = lane + 32 * i;
-      if (idx < dv) rec[2 + idx] = acc[i];
+    for (int a = 0; a < MAPS; ++a) {
+      float* r = rec + a * (dv + 2);
+      if (lane == 0) {
+        r[0] = m[a];
+        r[1] = l[a];
+      }
+#pragma unroll
+      for (int i = 0; i < MAX_W / 32; ++i) {
+        const int idx = lane + 32 * i;
+        if (idx < dv) r[2 + idx] = acc[a][i];
+      }
     }
     return;
   }
-  if (sink != nullptr) {
-    // the sink has a logit and nothing else: it joins the denominator once
-    const float s = sink[h] * LOG2E;
-    const float m_new = fmaxf(m, s);
-    const float alpha = exp2f(m - m_new);
-    l = l * alpha + exp2f(s - m_new);
+  float inv[MAPS];
 #pragma unroll
-    for (int i = 0; i < MAX_W / 32; ++i) acc[i] *= alpha;
-  }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-  T* orow = out + ((int64_t)t * nq + h) * dv;
+  for (int a = 0; a < MAPS; ++a) {
+    if (sink != nullptr) {
+      // the sink has a logit and nothing else: it joins the denominator once
+      const float sl = sink[h] * LOG2E;
+      const float m_new = fmaxf(m[a], sl);
+      const float alpha = exp2f(m[a] - m_new);
+      l[a] = l[a] * alpha + exp2f(sl - m_new);
 #pragma unroll
-  for (int i = 0; i < MAX_W / 32; ++i) {
-    const int idx = lane + 32 * i;
-    if (idx < dv) orow[idx] = from_f32<T>(acc[i] * inv);
+      for (int i = 0; i < MAX_W / 32; ++i) acc[a][i] *= alpha;
+    }
+    inv[a] = l[a] > 0.f ? 1.f / l[a] : 0.f;
   }
+  finish_head<T, MAPS>(acc, inv, finish, t, h, dv, out + ((int64_t)t * nq + h) * dv);
 }
 // A row's segments in segment order, then the sink, then the division.
-template <typename T>
+template <typename T, int MAPS>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_sink_merge_kernel(const float* __restrict__ partial, int segments, T* __restrict__ out,
                             const int* __restrict__ token_list, int tokens, int nq, int dv,
-                            const float* __restrict__ sink) {
+                            const float* __restrict__ sink, HeadFinish finish) {
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t wid = (int64_t)blockIdx.x * WARPS + warp;
   if (wid >= (int64_t)tokens * nq) return;
   const int t = token_list != nullptr ? token_list[wid / nq] : (int)(wid / nq), h = (int)(wid % nq);
-  float m = -INFINITY, l = 0.f;
-  float acc[MAX_W / 32];
+  float acc[MAPS][MAX_W / 32], inv[MAPS];
 #pragma unroll
-  for (int i = 0; i < MAX_W / 32; ++i) acc[i] = 0.f;
-  for (int s = 0; s < segments; ++s) {
-    const float* rec = partial + (wid * segments + s) * (int64_t)(dv + 2);
-    const float ms = rec[0], ls = rec[1];
-    if (ms == -INFINITY) continue;
-    const float m_new = fmaxf(m, ms);
-    const float a = exp2f(m - m_new), c = exp2f(ms - m_new);
-    l = l * a + ls * c;
+  for (int a = 0; a < MAPS; ++a) {
+    float m = -INFINITY, l = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_W / 32; ++i) {
-      const int idx = lane + 32 * i;
-      if (idx < dv) acc[i] = acc[i] * a + rec[2 + idx] * c;
+    for (int i = 0; i < MAX_W / 32; ++i) acc[a][i] = 0.f;
+    for (int s = 0; s < segments; ++s) {
+      const float* rec = partial + ((wid * segments + s) * MAPS + a) * (int64_t)(dv + 2);
+      const float ms = rec[0], ls = rec[1];
+      if (ms == -INFINITY) continue;
+      const float m_new = fmaxf(m, ms);
+      const float x = exp2f(m - m_new), c = exp2f(ms - m_new);
+      l = l * x + ls * c;
+#pragma unroll
+      for (int i = 0; i < MAX_W / 32; ++i) {
+        const int idx = lane + 32 * i;
+        if (idx < dv) acc[a][i] = acc[a][i] * x + rec[2 + idx] * c;
+      }
+      m = m_new;
     }
-    m = m_new;
-  }
-  if (sink != nullptr) {
-    const float s = sink[h] * LOG2E;
-    const float m_new = fmaxf(m, s);
-    const float a = exp2f(m - m_new);
-    l = l * a + exp2f(s - m_new);
+    if (sink != nullptr) {
+      const float s = sink[h] * LOG2E;
+      const float m_new = fmaxf(m, s);
+      const float x = exp2f(m - m_new);
+      l = l * x + exp2f(s - m_new);
 #pragma unroll
-    for (int i = 0; i < MAX_W / 32; ++i) acc[i] *= a;
+      for (int i = 0; i < MAX_W / 32; ++i) acc[a][i] *= x;
+    }
+    inv[a] = l > 0.f ? 1.f / l : 0.f;
   }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-  T* orow = out + ((int64_t)t * nq + h) * dv;
-#pragma unroll
-  for (int i = 0; i < MAX_W / 32; ++i) {
-    const int idx = lane + 32 * i;
-    if (idx < dv) orow[idx] = from_f32<T>(acc[i] * inv);
-  }
+  finish_head<T, MAPS>(acc, inv, finish, t, h, dv, out + ((int64_t)t * nq + h) * dv);
 }
 }  // namespace
 
@@ -373,49 +575,119 @@ VOSTI_API int vosti_qkv_store(const void* qkv, void* q_out, void* k_cache, void*
   VOSTI_LAUNCH_CHECK();
 }
 
-// q: [rows, nq, dk]; out: [rows, nq, dv]; bias: float32 [nq, bias_last + 1] in natural-log units
+static const HeadFinish NO_FINISH = {0.f, 1.f, 0.f, 0, nullptr, 0, 0};
+
+template <typename T, int MAPS>
+static cudaError_t attention_sink_launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* positions,
+                                         const int* request_of, const int* block_table, int max_pages, int page_size, int num_pages,
+                                         const int* token_list, int tokens, int nq, int nkv, int dk, int dv, float scale, int window,
+                                         const float* bias, int bias_last, const float* sink, float* partial, int segment,
+                                         int segments, unsigned* status, const HeadFinish& finish, cudaStream_t stream) {
+  const int64_t blocks = ((int64_t)tokens * nq + WARPS - 1) / WARPS;
+  const size_t smem = (size_t)WARPS * MAPS * dk * sizeof(float);
+  const dim3 grid((unsigned)blocks, segments > 1 ? segments : 1);
+  vosti_launch(attention_sink_kernel<T, MAPS>, grid, dim3(WARPS * 32), smem, stream, (const T*)q, (const T*)k_cache, (const T*)v_cache,
+               (T*)out, positions, request_of, block_table, max_pages, page_size, num_pages, token_list, tokens, nq, nkv, dk, dv,
+               scale * LOG2E, window, bias, bias_last, sink, partial, segment, status, finish);
+  if (segments > 1) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    vosti_launch(attention_sink_merge_kernel<T, MAPS>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, (const float*)partial,
+                 segments, (T*)out, token_list, tokens, nq, dv, sink, finish);
+  }
+  return cudaGetLastError();
+}
+
+// q: [rows, nq, maps, dk]; caches [pages, nkv, page_size, maps * dk | dv]; out: [rows, nq, dv]; bias: float32
+// [nq, bias_last + 1] in natural-log units
 // times log2(e), or null; sink: float32 [nq] in natural-log units, or null. `token_list` (or
 // null: all of them) names the `tokens` rows to compute. With `segments` > 1 the keys are cut
-// into pieces of `segment` keys (a multiple of 32) and `scratch` holds tokens * nq * segments *
-// (dv + 2) floats.
+// into pieces of `segment` keys (a multiple of 32) and `scratch` holds tokens * nq * segments * maps *
+// (dv + 2) floats. maps is 1 or 2 (see HeadFinish for what follows the softmax: lambda, the unit norm
+// with eps and out_scale, the gate).
+VOSTI_API int vosti_attention_maps(const void* q, const void* k_cache, const void* v_cache, void* out, const int* positions,
+                                   const int* request_of, const int* block_table, int max_pages, int page_size,
+                                   int num_pages, const int* token_list, int tokens, int nq, int nkv, int maps, int dk, int dv,
+                                   float scale, int window, const float* bias, int bias_last, const float* sink,
+                                   float* scratch, int segment, int segments, float lambda, int unit_norm, float eps,
+                                   float out_scale, const void* gate, int gate_f32, long long gate_stride, int is_f32,
+                                   unsigned* status, cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention: bad head counts nq=%d nkv=%d", nq, nkv);
+  VOSTI_REQUIRE(maps == 1 || maps == 2, "attention: one or two score maps a head, not %d", maps);
+  VOSTI_REQUIRE(dk > 0 && dv > 0 && dk <= MAX_W && dv <= MAX_W, "attention: head widths %d / %d must be at most %d", dk, dv, MAX_W);
+  VOSTI_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad cache geometry");
+  VOSTI_REQUIRE(bias == nullptr || bias_last >= 0, "attention: bad bias table");       // (window < 0: a chunk)
+  VOSTI_REQUIRE(segments >= 1 && segments <= 65535 && (segments == 1 || (scratch != nullptr && segment > 0 && segment % 32 == 0)),
+                "attention: key segments need scratch and a length that is a multiple of 32");
+  VOSTI_REQUIRE(gate == nullptr || gate_stride >= (long long)nq * dv, "attention: the gate's rows are narrower than the heads");
+  if (tokens == 0) return VOSTI_OK;
+  VOSTI_REQUIRE(((int64_t)tokens * nq + WARPS - 1) / WARPS <= 0x7fffffffLL, "attention: too many (token, head) pairs");
+  const HeadFinish finish = {lambda, out_scale, eps, unit_norm, gate, gate_f32, gate_stride};
+  float* partial = segments > 1 ? scratch : nullptr;
+  cudaError_t e;
+#define VOSTI_SINK_ARGS q, k_cache, v_cache, out, positions, request_of, block_table, max_pages, page_size, num_pages, token_list, \
+                        tokens, nq, nkv, dk, dv, scale, window, bias, bias_last, sink, partial, segment, segments, status, finish, stream
+  if (is_f32) e = maps == 2 ? attention_sink_launch<float, 2>(VOSTI_SINK_ARGS) : attention_sink_launch<float, 1>(VOSTI_SINK_ARGS);
+  else e = maps == 2 ? attention_sink_launch<bf16, 2>(VOSTI_SINK_ARGS) : attention_sink_launch<bf16, 1>(VOSTI_SINK_ARGS);
+#undef VOSTI_SINK_ARGS
+  if (e != cudaSuccess) { vosti_set_error("%s", cudaGetErrorString(e)); return (int)e; }
+  return VOSTI_OK;
+}
+
 VOSTI_API int vosti_attention_sink(const void* q, const void* k_cache, const void* v_cache, void* out, const int* positions,
                                    const int* request_of, const int* block_table, int max_pages, int page_size,
                                    int num_pages, const int* token_list, int tokens, int nq, int nkv, int dk, int dv,
                                    float scale, int window, const float* bias, int bias_last, const float* sink,
                                    float* scratch, int segment, int segments, int is_f32, unsigned* status,
                                    cudaStream_t stream) {
-  VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention: bad head counts nq=%d nkv=%d", nq, nkv);
-  VOSTI_REQUIRE(dk > 0 && dv > 0 && dk <= MAX_W && dv <= MAX_W, "attention: head widths %d / %d must be at most %d", dk, dv, MAX_W);
-  VOSTI_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad cache geometry");
-  VOSTI_REQUIRE(bias == nullptr || bias_last >= 0, "attention: bad bias table");       // (window < 0: a chunk)
-  VOSTI_REQUIRE(segments >= 1 && segments <= 65535 && (segments == 1 || (scratch != nullptr && segment > 0 && segment % 32 == 0)),
-                "attention: key segments need scratch and a length that is a multiple of 32");
+  return vosti_attention_maps(q, k_cache, v_cache, out, positions, request_of, block_table, max_pages, page_size, num_pages, token_list,
+                              tokens, nq, nkv, 1, dk, dv, scale, window, bias, bias_last, sink, scratch, segment, segments,
+                              NO_FINISH.lambda, 0, 0.f, 1.f, nullptr, 0, 0, is_f32, status, stream);
+}
+
+// a: [tokens, nq, maps, dv] attention outputs -> out [tokens, nq, dv] (see HeadFinish).
+VOSTI_API int vosti_head_finish(const void* a, void* out, int tokens, int nq, int maps, int dv, float lambda, int unit_norm, float eps,
+                                float out_scale, const void* gate, int gate_f32, long long gate_stride, int is_f32,
+                                cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && nq > 0 && dv > 0 && dv <= MAX_W && (maps == 1 || maps == 2), "head_finish: bad sizes");
+  VOSTI_REQUIRE(gate == nullptr || gate_stride >= (long long)nq * dv, "head_finish: the gate's rows are narrower than the heads");
   if (tokens == 0) return VOSTI_OK;
-  const int64_t warps = (int64_t)tokens * nq;
-  const int64_t blocks = (warps + WARPS - 1) / WARPS;
-  VOSTI_REQUIRE(blocks <= 0x7fffffffLL, "attention: too many (token, head) pairs");
-  const size_t smem = (size_t)WARPS * dk * sizeof(float);
-  float* partial = segments > 1 ? scratch : nullptr;
-  const dim3 grid((unsigned)blocks, segments > 1 ? segments : 1);
-  if (is_f32)
-    vosti_launch(attention_sink_kernel<float>, grid, dim3(WARPS * 32), smem, stream, (const float*)q,
-                 (const float*)k_cache, (const float*)v_cache, (float*)out, positions, request_of, block_table, max_pages,
-                 page_size, num_pages, token_list, tokens, nq, nkv, dk, dv, scale * LOG2E, window, bias, bias_last, sink,
-                 partial, segment, status);
-  else
-    vosti_launch(attention_sink_kernel<bf16>, grid, dim3(WARPS * 32), smem, stream, (const bf16*)q,
-                 (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions, request_of, block_table, max_pages,
-                 page_size, num_pages, token_list, tokens, nq, nkv, dk, dv, scale * LOG2E, window, bias, bias_last, sink,
-                 partial, segment, status);
-  if (segments > 1) {
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) { vosti_set_error("%s", cudaGetErrorString(e)); return (int)e; }
-    if (is_f32)
-      vosti_launch(attention_sink_merge_kernel<float>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
-                   (const float*)partial, segments, (float*)out, token_list, tokens, nq, dv, sink);
-    else
-      vosti_launch(attention_sink_merge_kernel<bf16>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
-                   (const float*)partial, segments, (bf16*)out, token_list, tokens, nq, dv, sink);
+  const HeadFinish f = {lambda, out_scale, eps, unit_norm, gate, gate_f32, gate_stride};
+  const unsigned blocks = (unsigned)(((int64_t)tokens * nq + WARPS - 1) / WARPS);
+  if (is_f32) {
+    if (maps == 2) vosti_launch(head_finish_kernel<float, 2>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const float*)a, (float*)out, tokens, nq, dv, f);
+    else vosti_launch(head_finish_kernel<float, 1>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const float*)a, (float*)out, tokens, nq, dv, f);
+  } else {
+    if (maps == 2) vosti_launch(head_finish_kernel<bf16, 2>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const bf16*)a, (bf16*)out, tokens, nq, dv, f);
+    else vosti_launch(head_finish_kernel<bf16, 1>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const bf16*)a, (bf16*)out, tokens, nq, dv, f);
   }
+  VOSTI_LAUNCH_CHECK();
+}
+
+// proj: [tokens, >= (nq * maps + nkv * maps) * dk + nkv * dv] float32 or bfloat16, rows proj_stride elements apart; bias float32
+// over the q | k | v columns, or null; q_norm / k_norm [dk] (float32 or bfloat16, both of one type), or null;
+// freq float32 [rot_half], or rot_half 0. Outputs in the serving type: q_out [tokens, nq * maps * dk];
+// caches [pages, nkv, page_size, maps * dk | dv] (null: queries only).
+VOSTI_API int vosti_qkv_heads(const void* proj, int proj_f32, long long proj_stride, const float* bias, void* q_out, void* k_cache,
+                              void* v_cache, const int* positions, const int* slot_mapping, int64_t num_slots, int page_size,
+                              int tokens, int nq, int nkv, int maps, int dk, int dv, const void* q_norm, const void* k_norm,
+                              int norm_f32, float eps, const float* freq, int rot_half, int interleaved, float magnitude,
+                              int is_f32, unsigned* status, cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv >= 0 && maps >= 1 && dk > 0 && dv > 0 && dk <= MAX_W && dv <= MAX_W, "qkv_heads: bad sizes");
+  VOSTI_REQUIRE(proj_stride >= (long long)(nq + nkv) * maps * dk + (long long)nkv * dv, "qkv_heads: the projection's rows are too narrow");
+  VOSTI_REQUIRE(k_cache == nullptr || (v_cache != nullptr && slot_mapping != nullptr && page_size > 0), "qkv_heads: a cache needs slots");
+  VOSTI_REQUIRE(rot_half >= 0 && 2 * rot_half <= dk && (rot_half == 0 || (freq != nullptr && positions != nullptr)),
+                "qkv_heads: the rotation takes at most the whole head and needs frequencies and positions");
+  if (tokens == 0) return VOSTI_OK;
+  const int threads = 256;
+  const size_t smem = ((size_t)2 * rot_half + (size_t)(threads / 32) * dk) * sizeof(float);
+  if (is_f32)
+    vosti_launch(qkv_heads_kernel<float>, dim3(tokens), dim3(threads), smem, stream, proj, proj_f32, (int64_t)proj_stride, bias, (float*)q_out,
+                 (float*)k_cache, (float*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, maps, dk, dv, q_norm, k_norm,
+                 norm_f32, eps, freq, rot_half, interleaved, magnitude, status);
+  else
+    vosti_launch(qkv_heads_kernel<bf16>, dim3(tokens), dim3(threads), smem, stream, proj, proj_f32, (int64_t)proj_stride, bias, (bf16*)q_out,
+                 (bf16*)k_cache, (bf16*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, maps, dk, dv, q_norm, k_norm,
+                 norm_f32, eps, freq, rot_half, interleaved, magnitude, status);
   VOSTI_LAUNCH_CHECK();
 }

@@ -9,10 +9,10 @@
 // sampler of the step before left on the device, which the host has not read yet.
 // `scale` multiplies the row in float32 (1: a plain copy), for architectures that scale
 // their embeddings.
-template <typename T>
+template <typename T, typename TO = T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restrict__ source,
                                  const int* __restrict__ values, const T* __restrict__ table,
-                                 T* __restrict__ out, int hidden, int vocab, float scale, unsigned* status) {
+                                 TO* __restrict__ out, int hidden, int vocab, float scale, unsigned* status) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -24,17 +24,17 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restr
     id = 0;
   }
   const T* src = table + (int64_t)id * hidden;
-  T* dst = out + (int64_t)t * hidden;
+  TO* dst = out + (int64_t)t * hidden;
   const int bytes = hidden * (int)sizeof(T);
-  if (scale != 1.f) {
+  if (scale != 1.f || sizeof(TO) != sizeof(T)) {
     for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-      dst[i] = bad ? from_f32<T>(0.f) : from_f32<T>(to_f32(src[i]) * scale);
+      dst[i] = bad ? from_f32<TO>(0.f) : from_f32<TO>(to_f32(src[i]) * scale);
   } else if (bytes % 16 == 0) {
     const int4* s4 = reinterpret_cast<const int4*>(src);
     int4* d4 = reinterpret_cast<int4*>(dst);
     for (int i = threadIdx.x; i < bytes / 16; i += blockDim.x) d4[i] = bad ? make_int4(0, 0, 0, 0) : s4[i];
   } else {
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = bad ? from_f32<T>(0.f) : src[i];
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = bad ? from_f32<TO>(0.f) : from_f32<TO>(to_f32(src[i]));
   }
 }
 
@@ -48,6 +48,20 @@ VOSTI_API int vosti_embedding(const int* ids, const int* source, const int* valu
     vosti_launch(embedding_kernel<float>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const float*)table, (float*)out, hidden, vocab, scale, status);
   else
     vosti_launch(embedding_kernel<bf16>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const bf16*)table, (bf16*)out, hidden, vocab, scale, status);
+  VOSTI_LAUNCH_CHECK();
+}
+
+// The same with float32 rows whatever the table's type: the start of a float32 residual stream
+// (a bfloat16 entry times the scale is not rounded again).
+VOSTI_API int vosti_embedding_stream(const int* ids, const int* source, const int* values, const void* table, float* out,
+                                     int tokens, int hidden, int vocab, int is_f32, float scale, unsigned* status,
+                                     cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes T=%d H=%d V=%d", tokens, hidden, vocab);
+  if (tokens == 0) return VOSTI_OK;
+  if (is_f32)
+    vosti_launch(embedding_kernel<float, float>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const float*)table, out, hidden, vocab, scale, status);
+  else
+    vosti_launch(embedding_kernel<bf16, float>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const bf16*)table, out, hidden, vocab, scale, status);
   VOSTI_LAUNCH_CHECK();
 }
 
@@ -313,6 +327,33 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     const float u = to_f32(gate_up[r * 2 * inter + inter + c]);
     out[i] = from_f32<T>(g * (1.f / (1.f + expf(-g))) * u);
   }
+}
+
+// act(gate) * up with act = relu (1) or the square of relu (2); same layout as silu_mul.
+template <typename T>
+__global__ void glu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t rows, int inter, int act) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t n = rows * inter;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / inter;
+    const int c = (int)(i - r * inter);
+    float g = fmaxf(to_f32(gate_up[r * 2 * inter + c]), 0.f);
+    if (act == 2) g *= g;
+    out[i] = from_f32<T>(g * to_f32(gate_up[r * 2 * inter + inter + c]));
+  }
+}
+
+VOSTI_API int vosti_glu_mul(const void* gate_up, void* out, int rows, int inter, int act, int is_f32, cudaStream_t stream) {
+  VOSTI_REQUIRE(rows >= 0 && inter > 0 && (act == 1 || act == 2), "glu_mul: bad sizes rows=%d inter=%d or activation %d", rows, inter, act);
+  if (rows == 0) return VOSTI_OK;
+  const int64_t n = (int64_t)rows * inter;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  if (is_f32)
+    vosti_launch(glu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out, (int64_t)rows, inter, act);
+  else
+    vosti_launch(glu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gate_up, (bf16*)out, (int64_t)rows, inter, act);
+  VOSTI_LAUNCH_CHECK();
 }
 
 VOSTI_API int vosti_silu_mul(const void* gate_up, void* out, int rows, int inter, int is_f32,

@@ -159,6 +159,58 @@ rms_stream_kernel(const float* stream, const void* t1, int t1_f32, const void* t
   }
 }
 
+// Norm after the sum, for blocks that norm what they have added: s = alpha * stream + t1 + t2 in
+// float32, y = s / sqrt(mean(s^2) + eps) * (offset + w); y is the new stream (float32, may be written
+// over the old one: a thread writes only what it read itself) and, rounded, the next sublayer's
+// input. The row is read twice, in the same order, so that any width works.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+post_norm_stream_kernel(const float* stream, float alpha, const void* __restrict__ t1, int t1_f32, const void* __restrict__ t2,
+                        int t2_f32, const void* __restrict__ weight, int w_f32, float offset, float eps, float* stream_out,
+                        TO* __restrict__ out, int width) {
+  __shared__ float scratch[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t base = (int64_t)blockIdx.x * width;
+  const bool vec = width % 4 == 0;
+  auto sum4 = [&](int i) {
+    float4 x = *reinterpret_cast<const float4*>(stream + base + i);
+    x = make_float4(x.x * alpha, x.y * alpha, x.z * alpha, x.w * alpha);
+    if (t1 != nullptr) { const float4 a = load_flex4(t1, t1_f32, base + i); x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
+    if (t2 != nullptr) { const float4 a = load_flex4(t2, t2_f32, base + i); x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
+    return x;
+  };
+  auto sum1 = [&](int i) { return (stream[base + i] * alpha + term_at(t1, t1_f32, base + i)) + term_at(t2, t2_f32, base + i); };
+  float ss = 0.f;
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      const float4 x = sum4(i);
+      ss += (x.x * x.x + x.y * x.y) + (x.z * x.z + x.w * x.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      const float x = sum1(i);
+      ss += x * x;
+    }
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      float4 x = sum4(i);
+      const float4 w = load_flex4(weight, w_f32, i);
+      x = make_float4(x.x * inv * (offset + w.x), x.y * inv * (offset + w.y), x.z * inv * (offset + w.z), x.w * inv * (offset + w.w));
+      if (stream_out != nullptr) *reinterpret_cast<float4*>(stream_out + base + i) = x;
+      if (out != nullptr) store4(out + base + i, x);
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float x = sum1(i) * inv * (offset + load_flex(weight, w_f32, i));
+    if (stream_out != nullptr) stream_out[base + i] = x;
+    if (out != nullptr) out[base + i] = from_f32<TO>(x);
+  }
+}
+
 constexpr int MAX_BRANCHES = 4;
 struct Branches {
   const void* x[MAX_BRANCHES];       // [rows, width], float32 or bfloat16
@@ -320,5 +372,23 @@ VOSTI_API int vosti_branch_sum(const void* const* xs, const int* x_f32, const fl
     br.scale[b] = scales[b];
   }
   vosti_launch(branch_sum_kernel, dim3(rows), dim3(256), 0, stream_id, br, out, width);
+  VOSTI_LAUNCH_CHECK();
+}
+
+// Norm after the sum (see post_norm_stream_kernel): stream float32 [rows, width]; t1, t2 (either may be
+// null) float32 or bfloat16; stream_out float32 (may be `stream`) and / or out in the output type.
+VOSTI_API int vosti_post_norm_stream(const float* stream, float alpha, const void* t1, int t1_f32, const void* t2, int t2_f32,
+                                     const void* weight, int w_f32, float offset, float eps, float* stream_out, void* out,
+                                     int out_f32, int rows, int width, cudaStream_t stream_id) {
+  VOSTI_REQUIRE(rows >= 0 && width > 0, "post_norm_stream: bad sizes rows=%d width=%d", rows, width);
+  VOSTI_REQUIRE(stream != nullptr && weight != nullptr, "post_norm_stream: a stream and a weight are needed");
+  VOSTI_REQUIRE(out != nullptr || stream_out != nullptr, "post_norm_stream: nowhere to write");
+  if (rows == 0) return VOSTI_OK;
+  if (out_f32)
+    vosti_launch(post_norm_stream_kernel<float>, dim3(rows), dim3(256), 0, stream_id, stream, alpha, t1, t1_f32, t2, t2_f32, weight,
+                 w_f32, offset, eps, stream_out, (float*)out, width);
+  else
+    vosti_launch(post_norm_stream_kernel<bf16>, dim3(rows), dim3(256), 0, stream_id, stream, alpha, t1, t1_f32, t2, t2_f32, weight,
+                 w_f32, offset, eps, stream_out, (bf16*)out, width);
   VOSTI_LAUNCH_CHECK();
 }

@@ -88,14 +88,24 @@ def _contig(*tensors):
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor,
-              feedback: Optional[tuple] = None, scale: float = 1.0) -> torch.Tensor:
+              feedback: Optional[tuple] = None, scale: float = 1.0, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """table[ids] * scale. `feedback` = (source, values), int32: row t takes values[source[t]] as
-    its id where source[t] >= 0 (a token sampled on the device that the host has not read yet)."""
+    its id where source[t] >= 0 (a token sampled on the device that the host has not read yet).
+    `out_dtype` float32 gives float32 rows from a bfloat16 table (the scaled entry is not rounded
+    again): the start of a float32 residual stream."""
     _contig(ids, table)
     source, values = feedback if feedback is not None else (None, None)
     if source is not None:
         _contig(source, values)
         assert source.shape[0] == ids.shape[0] and source.dtype == values.dtype == torch.int32
+    if out_dtype == torch.float32 and table.dtype != torch.float32:
+        out = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+        _check(library().vosti_embedding_stream(_p(ids), _p(source), _p(values), _p(table), _p(out), ids.shape[0], table.shape[1],
+                                                table.shape[0], _is_f32(table), ctypes.c_float(scale), _p(status), _stream()),
+               "embedding")
+        return out
+    if out_dtype is not None and out_dtype != table.dtype:
+        raise KernelError("embedding: rows come in the table's type or in float32")
     out = torch.empty((ids.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
     _check(library().vosti_embedding(_p(ids), _p(source), _p(values), _p(table), _p(out), ids.shape[0], table.shape[1],
                                      table.shape[0], _is_f32(table), ctypes.c_float(scale), _p(status), _stream()),
@@ -157,6 +167,23 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     out = torch.empty((gate_up.shape[0], inter), dtype=gate_up.dtype, device=gate_up.device)
     _check(library().vosti_silu_mul(_p(gate_up), _p(out), gate_up.shape[0], inter, _is_f32(gate_up),
                                     _stream()), "silu_mul")
+    return out
+
+
+GLU_ACTIVATIONS = {"silu": 0, "relu": 1, "relu2": 2}
+FUSED_GLU_ACTIVATIONS = ("silu",)         # those the tensor-core product's gated epilogue takes
+
+
+def glu_mul(gate_up: torch.Tensor, activation: str) -> torch.Tensor:
+    """act(gate) * up of a [rows, 2 * inter] product with the gate half first; `activation` is
+    "silu", "relu" or "relu2" (the square of relu)."""
+    if activation == "silu":
+        return silu_mul(gate_up)
+    _contig(gate_up)
+    inter = gate_up.shape[-1] // 2
+    out = torch.empty((gate_up.shape[0], inter), dtype=gate_up.dtype, device=gate_up.device)
+    _check(library().vosti_glu_mul(_p(gate_up), _p(out), gate_up.shape[0], inter, GLU_ACTIVATIONS[activation], _is_f32(gate_up),
+                                   _stream()), "glu_mul")
     return out
 
 
@@ -343,7 +370,7 @@ class PartialSum:
 
 
 def materialize(x):
-    return x.materialize() if isinstance(x, PartialSum) else x
+    return x.materialize() if isinstance(x, (PartialSum, StreamPair)) else x
 
 
 class PackedWeight:
@@ -379,7 +406,7 @@ class PackedWeight:
 
 
 def gemm_tc(x: torch.Tensor, w, status: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
-            swiglu: bool = False, allow_partial: bool = False):
+            swiglu: bool = False, allow_partial: bool = False, activation: str = "silu"):
     """y = x @ w.T on the tensor cores (bfloat16 operands, float32 accumulation); w is a
     [features, k] tensor or a `PackedWeight`. With `swiglu` the rows of w are blocks of 16 gate
     rows followed by their 16 up rows and y = silu(gate) * up has half as many columns."""
@@ -394,6 +421,8 @@ def gemm_tc(x: torch.Tensor, w, status: torch.Tensor, *, out_dtype: Optional[tor
         raise KernelError(f"gemm: inner sizes differ ({k} vs {w.shape[1]})")
     out_dtype = out_dtype or torch.bfloat16
     if swiglu:
+        if activation not in FUSED_GLU_ACTIVATIONS:
+            raise KernelError(f"gemm_tc: the gated epilogue takes {FUSED_GLU_ACTIVATIONS}, not '{activation}'")
         epilogue, width = EPI_SWIGLU, features // 2
         if out_dtype != torch.bfloat16:
             raise KernelError("gemm_tc: the fused SiLU*up epilogue writes bfloat16")
@@ -761,6 +790,39 @@ def rms_stream(x, weight: Optional[torch.Tensor], eps: float, out_dtype: Optiona
 
 
 # ---------------------------------------------------------------- token inputs
+class StreamPair:
+    """A float32 residual stream [rows, width] together with its rounding to the serving type: what a
+    block that norms after the sum hands to the next one (the sublayers' products read `rounded`,
+    the next sum reads `stream`). In float32 serving both are one tensor. `materialize` gives the stream."""
+
+    def __init__(self, rounded: torch.Tensor, stream: torch.Tensor):
+        self.rounded, self.stream = rounded, stream
+        self.shape = tuple(stream.shape)
+
+    def materialize(self) -> torch.Tensor:
+        return self.stream
+
+
+def post_norm_stream(stream: torch.Tensor, x, weight: torch.Tensor, alpha: float, eps: float, out_dtype: torch.dtype, *,
+                     offset: float = 0.0, in_place: bool = True) -> "StreamPair":
+    """Norm after the sum: s = alpha * stream + x in float32 (x: a tensor or a `DeferredSum`),
+    y = s / sqrt(mean(s^2) + eps) * (offset + weight). y becomes the stream (float32, written over the
+    old one with `in_place`) and, rounded to `out_dtype`, the next sublayer's input."""
+    terms, flat = _terms(x)
+    _contig(stream, weight)
+    if stream.dtype != torch.float32:
+        raise KernelError("post_norm_stream: the residual stream is float32")
+    rows, width = stream.shape
+    if any(tuple(t.shape) != (rows, width) for t in terms) or weight.shape[0] != width:
+        raise KernelError("post_norm_stream: the terms and the weight must match the stream's shape")
+    new = stream if in_place else torch.empty_like(stream)
+    out = None if out_dtype == torch.float32 else torch.empty((rows, width), dtype=out_dtype, device=stream.device)
+    _check(library().vosti_post_norm_stream(_p(stream), ctypes.c_float(alpha), *flat, _p(weight), _is_f32(weight),
+                                            ctypes.c_float(offset), ctypes.c_float(eps), _p(new), _p(out), 0, rows, width,
+                                            _stream()), "post_norm_stream")
+    return StreamPair(new if out is None else out, new)
+
+
 def pair_embedding(ids: torch.Tensor, table: torch.Tensor, pairs: torch.Tensor, last_token: torch.Tensor, ctx, *,
                    buckets: int, mul_prev: int, mul_cur: int, feedback: Optional[tuple] = None):
     """table[id] + pairs[(prev * mul_prev + id * mul_cur) % buckets] in float32, row `buckets` of
@@ -834,34 +896,115 @@ SINK_SEGMENT = int(_os.environ.get("VOSTI_SINK_SEGMENT", "256"))          # keys
 SINK_SPLIT_MAX_ROWS = 2048  # (token, head) rows up to which the keys are cut into segments
 
 
+class HeadFinish:
+    """What follows a head's softmax-weighted sum before the output projection, in float32 (the
+    kernels' HeadFinish): with two score maps a head o = a1 - `lam` * a2; with `unit_norm`
+    o / sqrt(mean(o^2) + eps) * out_scale over the head's values; with `gate` ([tokens, >= nq * dv],
+    float32 or bfloat16, rows may be strided: a view of a wider product) o * sigmoid(gate)."""
+
+    def __init__(self, *, lam: float = 0.0, unit_norm: bool = False, eps: float = 0.0, out_scale: float = 1.0,
+                 gate: Optional[torch.Tensor] = None):
+        self.lam, self.unit_norm, self.eps, self.out_scale, self.gate = float(lam), bool(unit_norm), float(eps), float(out_scale), gate
+        if gate is not None and (gate.dim() != 2 or gate.stride(1) != 1):
+            raise KernelError("head finish: the gate is [tokens, heads * width] with contiguous rows")
+
+    def args(self):
+        g = self.gate
+        return (ctypes.c_float(self.lam), int(self.unit_norm), ctypes.c_float(self.eps), ctypes.c_float(self.out_scale), _p(g),
+                0 if g is None else _is_f32(g), ctypes.c_longlong(0 if g is None else g.stride(0)))
+
+
+_NO_FINISH = HeadFinish()
+
+
+def head_finish(a: torch.Tensor, finish: "HeadFinish", *, nq: int, maps: int, dv: int) -> torch.Tensor:
+    """`finish` applied to attention outputs a [tokens, nq * maps * dv] that another kernel wrote;
+    returns [tokens, nq * dv]."""
+    _contig(a)
+    tokens = a.shape[0]
+    if a.shape[1] != nq * maps * dv:
+        raise KernelError("head_finish: the input's width does not match heads, maps and width")
+    out = torch.empty((tokens, nq * dv), dtype=a.dtype, device=a.device)
+    _check(library().vosti_head_finish(_p(a), _p(out), tokens, nq, maps, dv, *finish.args(), _is_f32(a), _stream()), "head_finish")
+    return out
+
+
+def qkv_heads(proj: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], *, nq: int, nkv: int,
+              maps: int = 1, dk: int, dv: int, page_size: int, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+              out_dtype: torch.dtype, status: torch.Tensor, bias: Optional[torch.Tensor] = None,
+              q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None, eps: float = 0.0,
+              freq: Optional[torch.Tensor] = None, interleaved: bool = False, magnitude: float = 1.0) -> torch.Tensor:
+    """After a q | k | v projection `proj` [tokens, >= (nq + nkv) * maps * dk + nkv * dv] (float32 or the
+    serving type; further columns may follow): `bias` (float32, over the q | k | v columns) is
+    added; every query and key head is RMS-normed with the weights `q_norm` / `k_norm` [dk] shared
+    by all heads; the first 2 * len(freq) elements of those heads turn by position * freq[i],
+    element i with i + len(freq), or 2i with 2i + 1 if `interleaved` (cos and sin times
+    `magnitude`); all in float32, rounded once to `out_dtype`. The queries are returned
+    [tokens, nq * maps * dk]; keys and values go to their cache slots ([pages, nkv, page_size,
+    maps * dk] and [pages, nkv, page_size, dv]). `maps` > 1: the projection holds `maps` query heads
+    a head and `maps` key heads a kv head, head by head."""
+    proj = materialize(proj)
+    _contig(k_cache, v_cache, positions, slot_mapping, freq, bias, q_norm, k_norm)
+    tokens = proj.shape[0]
+    width = (nq + nkv) * maps * dk + nkv * dv
+    if proj.dim() != 2 or proj.stride(1) != 1 or proj.shape[1] < width:
+        raise KernelError("qkv_heads: the projection is [tokens, >= q | k | v columns] with contiguous rows")
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape[0] != width):
+        raise KernelError("qkv_heads: the bias is float32 over the q | k | v columns")
+    if freq is not None and freq.dtype != torch.float32:
+        raise KernelError("qkv_heads: rotation frequencies are float32")
+    norm_flag = 0
+    if q_norm is not None or k_norm is not None:
+        norm_flag = _is_f32(q_norm if q_norm is not None else k_norm)
+        if q_norm is not None and k_norm is not None and _is_f32(q_norm) != _is_f32(k_norm):
+            raise KernelError("qkv_heads: q and k norm weights must share a dtype")
+    for cache in (k_cache, v_cache):
+        if cache is not None and cache.dtype != out_dtype:
+            raise KernelError("qkv_heads: the caches hold the output type")
+    q = torch.empty((tokens, nq * maps * dk), dtype=out_dtype, device=proj.device)
+    num_slots = 0 if k_cache is None else k_cache.numel() // (nkv * maps * dk)
+    _check(library().vosti_qkv_heads(_p(proj), _is_f32(proj), ctypes.c_longlong(proj.stride(0)), _p(bias), _p(q), _p(k_cache),
+                                     _p(v_cache), _p(positions), _p(slot_mapping), ctypes.c_int64(num_slots), page_size, tokens,
+                                     nq, nkv, maps, dk, dv, _p(q_norm), _p(k_norm), norm_flag, ctypes.c_float(eps), _p(freq),
+                                     0 if freq is None else freq.shape[0], int(bool(interleaved)), ctypes.c_float(magnitude),
+                                     1 if out_dtype == torch.float32 else 0, _p(status), _stream()), "qkv_heads")
+    return q
+
+
 def _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, *, token_list, count, nq, nkv, dk, dv, scale, window,
-                         bias, sink) -> None:
+                         bias, sink, maps=1, finish=None) -> None:
     """The CUDA-core kernel over `count` rows of the step (all of them if `token_list` is None)."""
     flag = _same_dtype(q, k_cache, v_cache)
-    num_pages = k_cache.numel() // (group.page_size * nkv * dk)
+    num_pages = k_cache.numel() // (group.page_size * nkv * maps * dk)
     segments, scratch = 1, None
     if count * nq <= SINK_SPLIT_MAX_ROWS and ctx.max_kv_len > SINK_SEGMENT:
         segments = -(-ctx.max_kv_len // SINK_SEGMENT)
-        scratch = _workspace(q.device, count * nq * segments * (dv + 2))
-    _check(library().vosti_attention_sink(
+        scratch = _workspace(q.device, count * nq * segments * maps * (dv + 2))
+    _check(library().vosti_attention_maps(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ctx.positions), _p(ctx.request_of), _p(group.block_table),
-        group.block_table.shape[1], group.page_size, num_pages, _p(token_list), count, nq, nkv, dk, dv,
+        group.block_table.shape[1], group.page_size, num_pages, _p(token_list), count, nq, nkv, maps, dk, dv,
         ctypes.c_float(scale), window, _p(bias), 0 if bias is None else bias.shape[1] - 1, _p(sink), _p(scratch),
-        SINK_SEGMENT, segments, flag, _p(ctx.status), _stream()), "attention_sink", kernels=2 if segments > 1 else 1)
+        SINK_SEGMENT, segments, *(finish or _NO_FINISH).args(), flag, _p(ctx.status), _stream()), "attention_sink",
+        kernels=2 if segments > 1 else 1)
 
 
 def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, *, nq: int, nkv: int,
                    dk: int, dv: int, scale: float, window: int, bias: Optional[torch.Tensor],
-                   sink: Optional[torch.Tensor], chunk: int = 0) -> torch.Tensor:
+                   sink: Optional[torch.Tensor], chunk: int = 0, maps: int = 1,
+                   finish: Optional["HeadFinish"] = None) -> torch.Tensor:
     """Causal attention of every query row over its request's cached keys (the last `window` of
     them, or with `chunk` those of the query's own chunk of positions), with an optional bias
     table float32 [nq, distances] (base-2 units, the last column serving every larger distance)
     and an optional sink logit per head (float32 [nq], natural units). Returns [tokens, nq * dv].
-    bfloat16 with equal key and value widths of 64 or 128 (pages of a multiple of 16 tokens, at
-    most 16 query heads per kv head): long rows run on the tensor-memory kernel and requests that
-    bring a few tokens on the split-key decode kernels, as Qwen3's do, both with the bias and the
-    sink. Everything else runs on the CUDA-core kernel, with the keys cut into segments when the
-    step has few rows."""
+    With `maps` = 2 a head has two score maps (queries [tokens, nq, 2, dk], the key cache's entries
+    2 * dk wide) over the same values; `finish` (a `HeadFinish`) says how they are combined and what
+    else follows the softmax (unit norm, gate).
+    bfloat16 with one map and equal key and value widths of 64 or 128 (pages of a multiple of 16
+    tokens, at most 16 query heads per kv head): long rows run on the tensor-memory kernel and
+    requests that bring a few tokens on the split-key decode kernels, as Qwen3's do, both with the
+    bias and the sink, and `finish` is a kernel of its own after them. Everything else runs on the
+    CUDA-core kernel, with the keys cut into segments when the step has few rows, and `finish` is
+    its last step."""
     _contig(q, k_cache, v_cache, bias, sink)
     tokens = q.shape[0]
     out = torch.empty((tokens, nq * dv), dtype=q.dtype, device=q.device)
@@ -870,10 +1013,10 @@ def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     window = -chunk if chunk else window            # the kernels take a chunk as a negative window
     common = dict(nq=nq, nkv=nkv, dk=dk, dv=dv, scale=scale, window=window, bias=bias, sink=sink)
     lib = library()
-    tensor_memory = (q.dtype == torch.bfloat16 and dk == dv and nq // nkv <= 16
+    tensor_memory = (q.dtype == torch.bfloat16 and dk == dv and nq // nkv <= 16 and maps == 1
                      and lib.vosti_attention_prefill_tc_supported(dk, group.page_size))
     if not tensor_memory or getattr(ctx, "layout", None) is None or "attention" not in ctx.layout:
-        _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, token_list=None, count=tokens, **common)
+        _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, token_list=None, count=tokens, maps=maps, finish=finish, **common)
         return out
     # as for `attention`: requests that bring a few tokens one query at a time with split keys,
     # longer portions tile by tile on the tensor-memory kernel (the step's work lists)
@@ -897,6 +1040,8 @@ def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
             _p(ctx.cu_q), _p(ctx.kv_len), _p(group.block_table), group.block_table.shape[1], group.page_size, num_pages,
             nq, nkv, dk, lists["max_long_q_len"], tokens, ctypes.c_float(scale), window, _p(bias), bias_last, _p(sink),
             _p(ctx.status), _stream()), "attention_prefill_tc_biased")
+    if finish is not None:
+        return head_finish(out, finish, nq=nq, maps=1, dv=dv)
     return out
 
 
@@ -1223,14 +1368,69 @@ def moe_router(x: torch.Tensor, router: torch.Tensor, top: int, *, over_all: boo
     return (chosen, weights, dense, logits) if want_logits else (chosen, weights, dense)
 
 
-def moe_scale(act: torch.Tensor, dense: Optional[torch.Tensor], ff: int, *, gelu: bool = False) -> torch.Tensor:
+def moe_router_scored(x: torch.Tensor, router: torch.Tensor, top: int, *, identity: int = 0,
+                      correction: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1, gate_row: bool = False,
+                      scale: float = 1.0, want_logits: bool = False):
+    """Router product and choice by corrected scores in one kernel. `router` is float32
+    [routed + (1 if gate_row), k]: `routed` rows take part in the choice, of which the last
+    `identity` are experts that return their input. s = softmax over the routed logits; rows are
+    chosen by s + correction (float32 [routed]) inside the `keep` best of `groups` equal groups of
+    neighbouring rows (a group's score: its largest corrected score); weights = the chosen rows' s
+    divided by their sum (+ 1e-20), times `scale`. Returns (chosen int32 [tokens, top], weights
+    float32 [tokens, top], dense float32 [tokens, routed - identity + (1 if gate_row)], ident float32
+    [tokens] or None): dense holds the chosen experts' weights and, with `gate_row`, in its last
+    column the sigmoid of the gate row's logit; ident is the sum of the chosen identity experts' weights."""
+    x = materialize(x)
+    _contig(x, router, correction)
+    rows = router.shape[0]
+    routed = rows - int(gate_row)
+    if router.dtype != torch.float32 or router.shape[1] != x.shape[1]:
+        raise KernelError("moe_router: the router is float32 [rows, k]")
+    if correction is not None and (correction.dtype != torch.float32 or correction.shape[0] != routed):
+        raise KernelError("moe_router: the correction is float32 [routed]")
+    tokens = x.shape[0]
+    chosen = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
+    dense = torch.empty((tokens, routed - identity + int(gate_row)), dtype=torch.float32, device=x.device)
+    ident = torch.empty((tokens,), dtype=torch.float32, device=x.device) if identity else None
+    logits = torch.empty((tokens, rows), dtype=torch.float32, device=x.device) if want_logits else None
+    _check(library().vosti_moe_router_scored(_p(x), _is_f32(x), _p(router), tokens, routed, identity, x.shape[1], top,
+                                             _p(correction), groups, keep, int(gate_row), ctypes.c_float(scale), _p(chosen),
+                                             _p(weights), _p(dense), _p(ident), _p(logits), _stream()), "moe_router_scored")
+    return (chosen, weights, dense, ident, logits) if want_logits else (chosen, weights, dense, ident)
+
+
+MOE_ACTIVATIONS = {None: 0, "gelu": 1, "relu2": 2}
+
+
+def moe_scale(act: torch.Tensor, dense: Optional[torch.Tensor], ff: int, *, gelu: bool = False,
+              activation: Optional[str] = None, tail: int = 0) -> torch.Tensor:
     """act[t, e * ff + i] <- f(act[t, e * ff + i]) * dense[t, e], in place; f is the exact GELU with
-    `gelu`, else the identity; without `dense` the activation alone."""
+    `gelu` (or `activation` "gelu"), the square of relu with `activation` "relu2", else the identity;
+    without `dense` the activation alone. With `tail` the row ends in one more slice of `tail`
+    columns, weighted by dense's last column."""
     _contig(act, dense)
-    experts = dense.shape[1] if dense is not None else act.shape[1] // ff
-    _check(library().vosti_moe_scale(_p(act), _p(dense), act.shape[0], experts, ff, _is_f32(act), int(gelu), _stream()),
+    mode = 1 if gelu else MOE_ACTIVATIONS[activation]
+    if tail == 0 and mode < 2:
+        experts = dense.shape[1] if dense is not None else act.shape[1] // ff
+        _check(library().vosti_moe_scale(_p(act), _p(dense), act.shape[0], experts, ff, _is_f32(act), mode, _stream()),
+               "moe_scale")
+        return act
+    experts = (act.shape[1] - tail) // ff
+    if experts * ff + tail != act.shape[1] or (dense is not None and dense.shape[1] != experts + (1 if tail else 0)):
+        raise KernelError("moe_scale: the activation's width does not match the experts, their width and the tail")
+    _check(library().vosti_moe_scale_tail(_p(act), _p(dense), act.shape[0], experts, ff, tail, _is_f32(act), mode, _stream()),
            "moe_scale")
     return act
+
+
+def moe_identity(y: torch.Tensor, coeff: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """y[t] += coeff[t] * x[t] in place (y float32): the share of experts that return their input."""
+    _contig(y, coeff, x)
+    if y.dtype != torch.float32 or coeff.dtype != torch.float32 or tuple(x.shape) != tuple(y.shape):
+        raise KernelError("moe_identity: y and the coefficients are float32, x has y's shape")
+    _check(library().vosti_moe_identity(_p(y), _p(coeff), _p(x), _is_f32(x), y.shape[0], y.shape[1], _stream()), "moe_identity")
+    return y
 
 
 def moe_group(chosen: torch.Tensor, experts: int):

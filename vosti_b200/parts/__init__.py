@@ -14,7 +14,7 @@ from .selective_scan import SelectiveScan
 from .token_input import GatedTokenInput
 from .branches import BranchMixer
 from .reentry import ConcatReentry
-from .block import ParallelBlock, PreNormBlock, SandwichStreamBlock, StreamPreNormBlock, build_block
+from .block import ParallelBlock, PostNormStreamBlock, PreNormBlock, SandwichStreamBlock, StreamPreNormBlock, build_block
 from .embedding import PairHashEmbedding, TableEmbedding
 from .head import LinearHead
 
@@ -24,5 +24,5 @@ __all__ = [
     "register_part", "register_step_layout", "unregister_part", "linear", "RMSNorm", "RotaryEncoding", "Attention",
     "SwiGLU", "PreNormBlock", "build_block", "build_reentry", "DynamicTanh", "ExpertMixture", "SinkAttention",
     "GatedDeltaRule", "BranchMixer", "ConcatReentry", "ParallelBlock", "StreamRMSNorm", "GeneralDeltaRule",
-    "GatedTokenInput", "StreamPreNormBlock", "LayerNormStream", "LatentAttention", "SelectiveScan", "SandwichStreamBlock", "PairHashEmbedding", "TokenInput", "build_token_input",
+    "GatedTokenInput", "StreamPreNormBlock", "LayerNormStream", "LatentAttention", "SelectiveScan", "SandwichStreamBlock", "PostNormStreamBlock", "PairHashEmbedding", "TokenInput", "build_token_input",
 ]

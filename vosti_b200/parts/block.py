@@ -294,3 +294,64 @@ class SandwichStreamBlock(StreamPreNormBlock):
 
 
 register_part("arrangement", "sandwich_stream", SandwichStreamBlock, replace=True)
+
+
+class PostNormStreamBlock(StreamPreNormBlock):
+    """'post_norm_stream': the norm comes after the sum, over a float32 residual stream,
+
+        x <- norm1(alpha * x + mixer(x));   x <- norm2(alpha * x + ff(x))
+
+    with one constant alpha for the model (`LayerSpec.norm` parameter `alpha`, default 1; the other
+    parameters are those of a root-mean-square norm: `eps`, `unit_offset`). The sublayers read x
+    itself, rounded to the serving type. One kernel per sublayer boundary scales the stream, adds
+    the sublayer's float32 output, norms, and writes the new stream and its rounding
+    (`ops.post_norm_stream`); a block hands the next one both (`ops.StreamPair`) and no residual,
+    so the model's final norm reads the stream alone. A layer without a feed-forward has no
+    second step; a checkpoint may carry its norm all the same.
+
+    Checkpoint names: `LayerSpec.names` maps the roles "input_norm" (norm1), "post_norm" (norm2),
+    "mixer", "feed_forward" to name fragments; a norm's `weight` tensor is called by the fragment
+    itself, every other tensor `<fragment>.<key>`."""
+
+    def __init__(self, spec: LayerSpec, hidden_size: int):
+        super().__init__(spec, hidden_size)
+        if spec.token_input is not None or spec.out_norm is not None or spec.layer_scale:
+            raise ConfigError("post_norm_stream block: it takes no token input, output norm or layer scale")
+        self.alpha = float(spec.norm.get("alpha", 1.0))
+        if self.post_norm is None:
+            self.unused_post_norm = build_norm(spec.norm, hidden_size)
+        for norm in (self.input_norm, self.post_norm):
+            if norm is not None and not hasattr(norm, "offset"):
+                raise ConfigError("post_norm_stream block: the norm must be a root-mean-square norm over the stream (rms_stream)")
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        import dataclasses
+        specs = super().weight_specs()
+        if self.feed_forward is None:
+            fragment = self.spec.name_of("post_norm")
+            for key, w in self.unused_post_norm.weight_specs().items():
+                specs[fragment if key == "weight" else f"{fragment}.{key}"] = dataclasses.replace(w, optional=True)
+        return specs
+
+    def _after(self, ctx, norm, pair, y):
+        return ops.post_norm_stream(pair.stream, y, norm.weight, self.alpha, norm.eps, ctx.dtype, offset=norm.offset)
+
+    def forward(self, ctx, hidden, residual, cache, writes_cache=True):
+        if residual is not None:
+            raise ConfigError("post_norm_stream block: the block before it left a residual; it follows blocks of its own kind")
+        if isinstance(hidden, ops.StreamPair):
+            pair = hidden
+        else:
+            # the embedding's rows start the stream: float32 rows as they are, others widened
+            hidden = ops.materialize(hidden)
+            stream = hidden if hidden.dtype == torch.float32 else ops.stream_sum(None, hidden)
+            rounded = stream if ctx.dtype == torch.float32 else (
+                hidden if hidden.dtype == ctx.dtype else ops.stream_sum(stream, None, out_dtype=ctx.dtype))
+            pair = ops.StreamPair(rounded, stream)
+        pair = self._after(ctx, self.input_norm, pair, self.mixer.forward(ctx, pair.rounded, cache, writes_cache))
+        if self.feed_forward is not None:
+            pair = self._after(ctx, self.post_norm, pair, self.feed_forward.forward(ctx, pair.rounded))
+        return pair, None
+
+
+register_part("arrangement", "post_norm_stream", PostNormStreamBlock, replace=True)

@@ -1,6 +1,7 @@
 """The embedding table: hidden rows by token id (kernels/triton_kernels/embedding.py:62-84),
 optionally multiplied by a constant `scale` in float32 (Qwen3 has none; architectures that
-scale their embeddings by sqrt(hidden) name it in their spec).
+scale their embeddings by sqrt(hidden) name it in their spec). `out_dtype` "float32" gives float32
+rows whatever the table's type: the start of a float32 residual stream.
 """
 from __future__ import annotations
 
@@ -20,6 +21,7 @@ class TableEmbedding(Embedding):
         self.scale = float(spec.get("scale", 1.0) or 1.0)
         if not self.scale == self.scale or self.scale in (float("inf"), float("-inf")):
             raise ConfigError("embedding: scale must be a finite number")
+        self.out_dtype = torch.float32 if spec.get("out_dtype") == "float32" else None
         self.weight = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
@@ -32,7 +34,7 @@ class TableEmbedding(Embedding):
         return self.weight
 
     def forward(self, ctx, tokens, feedback=None):
-        return ops.embedding(tokens, self.weight, ctx.status, feedback=feedback, scale=self.scale)
+        return ops.embedding(tokens, self.weight, ctx.status, feedback=feedback, scale=self.scale, out_dtype=self.out_dtype)
 
 
 register_part("embedding", "table", TableEmbedding, replace=True)

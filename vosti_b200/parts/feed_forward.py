@@ -6,14 +6,17 @@ single product, as the reference's loader concatenates them
 gate * sigmoid(gate) * up in float32 (kernels/triton_kernels/silu_mul.py:66-87).
 
 Parameters besides `intermediate_size`: `tensor_names`, the checkpoint's names of the gate, up
-and down matrices (default: Qwen3's), and `float32_out`, for models whose residual stream is
-float32: the down projection is then not rounded to the serving type.
+and down matrices (default: Qwen3's), `float32_out`, for models whose residual stream is
+float32: the down projection is then not rounded to the serving type, and `activation`: "silu"
+(the default), "relu" or "relu2" (the square of relu) on the gate.
 
 `ExpertMixture` is the same feed-forward as `experts` small ones, of which each token uses
 the `top` with the largest router logits, weighted by the softmax over the chosen logits only.
 Its experts may also be plain two-matrix feed-forwards, down(gelu(up(x))) with the exact (erf)
 GELU, and its weights the chosen experts' shares of a softmax over all experts, divided by
-their sum and multiplied by a constant.
+their sum and multiplied by a constant. A third way of routing ("scored") chooses by corrected
+softmax scores inside the best groups of experts, may count experts that return their input
+among the routed ones, and may add a shared expert behind a per-token gate (see the class).
 """
 from __future__ import annotations
 
@@ -28,7 +31,7 @@ from .base import FeedForward, register_part
 from .linear import linear, prepare_weight, uses_tensor_cores
 
 
-def stack_gate_up(gate: torch.Tensor, up: torch.Tensor, dtype: torch.dtype):
+def stack_gate_up(gate: torch.Tensor, up: torch.Tensor, dtype: torch.dtype, activation: str = "silu"):
     """One [2I, hidden] matrix for the gate and up projections, and whether SiLU(gate)*up can be
     the tensor-core product's epilogue. If so, rows are laid out as blocks of 16 gate rows
     followed by their 16 up rows, so that both halves of an output land in one warp's slice of
@@ -36,7 +39,8 @@ def stack_gate_up(gate: torch.Tensor, up: torch.Tensor, dtype: torch.dtype):
     inter = gate.shape[0]
     common = torch.float32 if torch.float32 in (gate.dtype, up.dtype) else gate.dtype
     stacked = torch.cat([gate.to(common), up.to(common)], dim=0)
-    fused = dtype == torch.bfloat16 and inter % 16 == 0 and uses_tensor_cores(dtype, stacked)
+    fused = (dtype == torch.bfloat16 and inter % 16 == 0 and uses_tensor_cores(dtype, stacked)
+             and activation in ops.FUSED_GLU_ACTIVATIONS)
     if not fused:
         return stacked.contiguous(), False
     h = stacked.shape[1]
@@ -44,10 +48,10 @@ def stack_gate_up(gate: torch.Tensor, up: torch.Tensor, dtype: torch.dtype):
     return prepare_weight(blocks.reshape(2 * inter, h).contiguous(), dtype), True
 
 
-def gated_activation(ctx, x, w_gate_up, fused: bool):
+def gated_activation(ctx, x, w_gate_up, fused: bool, activation: str = "silu"):
     if fused:
-        return ops.gemm_tc(ops.materialize(x), w_gate_up, ctx.status, swiglu=True)
-    return ops.silu_mul(linear(ctx, x, w_gate_up))
+        return ops.gemm_tc(ops.materialize(x), w_gate_up, ctx.status, swiglu=True, activation=activation)
+    return ops.glu_mul(ops.materialize(linear(ctx, x, w_gate_up)), activation)
 
 
 class SwiGLU(FeedForward):
@@ -58,6 +62,9 @@ class SwiGLU(FeedForward):
             raise ConfigError("swiglu: intermediate_size must be positive")
         self.names = tuple(spec.get("tensor_names") or ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
         self.float32_out = bool(spec.get("float32_out", False))
+        self.activation = str(spec.get("activation", "silu") or "silu")
+        if self.activation not in ops.GLU_ACTIVATIONS:
+            raise ConfigError(f"swiglu: activation is one of {sorted(ops.GLU_ACTIVATIONS)}")
         self.w_gate_up = self.w_down = None
         self.fused = False
 
@@ -69,13 +76,13 @@ class SwiGLU(FeedForward):
     def load(self, tensors, dtype):
         gate, up, down = self.names
         self.w_down = prepare_weight(tensors[down], dtype)
-        self.w_gate_up, self.fused = stack_gate_up(tensors[gate], tensors[up], dtype)
+        self.w_gate_up, self.fused = stack_gate_up(tensors[gate], tensors[up], dtype, self.activation)
 
     def first_weight(self):
         return self.w_gate_up
 
     def forward(self, ctx, x):
-        mlp = gated_activation(ctx, x, self.w_gate_up, self.fused)
+        mlp = gated_activation(ctx, x, self.w_gate_up, self.fused, self.activation)
         if self.float32_out:
             return linear(ctx, mlp, self.w_down, out_dtype=torch.float32)
         return linear(ctx, mlp, self.w_down, allow_partial=True)     # summed by the norm that follows
@@ -91,6 +98,20 @@ class ExpertMixture(FeedForward):
     ("top_softmax", the default: softmax over the chosen logits; "softmax_renorm": softmax over
     all experts, the chosen scores divided by their sum + 1e-20) and `scale`, a constant on the
     weights (default 1).
+
+    With `route` "scored" (experts without a gate only): the router has experts + `identity` rows;
+    scores are s = softmax over all of them; rows are chosen by s + `correction` (a tensor,
+    present if `correction` is true), among the rows of the `keep` best of `groups` equal groups of
+    neighbouring rows (a group's score is its largest corrected score; the other groups' rows count as
+    minus infinity); the weights are the chosen rows' s divided by their sum + 1e-20, times `scale`.
+    The last `identity` rows are experts without tensors whose output is the feed-forward's input
+    itself. `shared` > 0 adds a shared expert of that width (`shared.up`, `shared.down`, same form as
+    the others) that runs for every token and is multiplied by sigmoid(w_sg . x), one number per
+    token (`shared.sg` [1, hidden]). `activation` ("gelu" by default for experts without a gate, or
+    "relu2", the square of relu) is the experts' and the shared expert's. The shared expert's matrices
+    stand beside the experts' in the stacked matrices, its gate row under the router's rows, so the
+    whole feed-forward is the router kernel, two products, the scaling pass and, with identity experts,
+    one pass that adds their share of the input.
 
     The router's logits are float32. The experts' gate and up matrices stand side by side as one
     [2 * experts * I, hidden] matrix and their down matrices as one [hidden, experts * I]: every
@@ -115,16 +136,38 @@ class ExpertMixture(FeedForward):
         self.float32_out = bool(spec.get("float32_out", False))
         self.gated = bool(spec.get("gated", True))
         self.route, self.scale = spec.get("route", "top_softmax"), float(spec.get("scale", 1.0))
-        if self.experts <= 0 or not 0 < self.top <= self.experts or self.inter <= 0:
+        self.identity = int(spec.get("identity", 0) or 0)
+        self.has_correction = bool(spec.get("correction", False))
+        self.groups, self.keep = int(spec.get("groups", 1) or 1), int(spec.get("keep", 1) or 1)
+        self.shared = int(spec.get("shared", 0) or 0)
+        self.activation = spec.get("activation") or ("gelu" if not self.gated else None)
+        self.correction = None
+        if self.experts <= 0 or not 0 < self.top <= self.experts + self.identity or self.inter <= 0:
             raise ConfigError("moe: experts, top (at most experts) and intermediate_size must be positive")
-        if self.route not in ("top_softmax", "softmax_renorm") or self.scale != self.scale:
-            raise ConfigError("moe: route is 'top_softmax' or 'softmax_renorm' and scale a number")
+        if self.route not in ("top_softmax", "softmax_renorm", "scored") or self.scale != self.scale:
+            raise ConfigError("moe: route is 'top_softmax', 'softmax_renorm' or 'scored' and scale a number")
+        if self.route != "scored" and (self.identity or self.has_correction or self.groups != 1 or self.shared
+                                       or self.activation not in (None, "gelu")):
+            raise ConfigError("moe: identity experts, a correction, groups, a shared expert and other activations need route 'scored'")
+        if self.route == "scored":
+            routed = self.experts + self.identity
+            if self.gated or self.activation not in ("gelu", "relu2"):
+                raise ConfigError("moe: route 'scored' takes experts without a gate, with activation 'gelu' or 'relu2'")
+            if self.identity < 0 or self.shared < 0 or self.groups < 1 or routed % self.groups or not 1 <= self.keep <= self.groups:
+                raise ConfigError("moe: groups must divide experts + identity, and keep lie between 1 and groups")
+            if self.top > routed // self.groups * self.keep:
+                raise ConfigError("moe: top exceeds the experts of the kept groups")
         self.router = self.w_gate_up = self.w_down = None
         self.fused = False
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         h, i = self.hidden_size, self.inter
-        specs = {"router": WeightSpec((self.experts, h), std=0.5)}
+        specs = {"router": WeightSpec((self.experts + self.identity, h), std=0.5)}
+        if self.has_correction:
+            specs["correction"] = WeightSpec((self.experts + self.identity,), std=0.05)
+        if self.shared:
+            specs.update({"shared.up": WeightSpec((self.shared, h)), "shared.down": WeightSpec((h, self.shared)),
+                          "shared.sg": WeightSpec((1, h), std=0.5)})
         for e in range(self.experts):
             specs.update({f"e{e}.up": WeightSpec((i, h)), f"e{e}.down": WeightSpec((h, i))})
             if self.gated:
@@ -133,6 +176,8 @@ class ExpertMixture(FeedForward):
 
     def load(self, tensors, dtype):
         self.router = tensors["router"].float().contiguous()        # 32-bit logits from exact 32-bit products
+        if self.route == "scored":
+            return self._load_scored(tensors, dtype)
         up = torch.cat([tensors[f"e{e}.up"] for e in range(self.experts)], dim=0)
         if self.gated:
             gate = torch.cat([tensors[f"e{e}.gate"] for e in range(self.experts)], dim=0)
@@ -148,6 +193,31 @@ class ExpertMixture(FeedForward):
                 else:
                     gate_up, fused = prepare_weight(tensors[f"e{e}.up"], dtype), False
                 self.per_expert.append((gate_up, fused, prepare_weight(tensors[f"e{e}.down"], dtype)))
+
+    def _load_scored(self, tensors, dtype):
+        ups = [tensors[f"e{e}.up"] for e in range(self.experts)]
+        downs = [tensors[f"e{e}.down"] for e in range(self.experts)]
+        if self.shared:
+            # the shared expert beside the others; its gate row under the router's
+            ups.append(tensors["shared.up"])
+            downs.append(tensors["shared.down"])
+            self.router = torch.cat([self.router, tensors["shared.sg"].float().reshape(1, -1)], dim=0).contiguous()
+        if self.has_correction:
+            self.correction = tensors["correction"].float().contiguous()
+        self.w_gate_up, self.fused = prepare_weight(torch.cat(ups, dim=0).contiguous(), dtype), False
+        self.w_down = prepare_weight(torch.cat(downs, dim=1).contiguous(), dtype)
+        self.per_expert = []
+
+    def _forward_scored(self, ctx, x):
+        chosen, weights, dense, ident = ops.moe_router_scored(
+            x, self.router, self.top, identity=self.identity, correction=self.correction, groups=self.groups, keep=self.keep,
+            gate_row=bool(self.shared), scale=self.scale)
+        act = ops.moe_scale(ops.materialize(linear(ctx, x, self.w_gate_up)), dense, self.inter, activation=self.activation,
+                            tail=self.shared)
+        y = linear(ctx, act, self.w_down, out_dtype=torch.float32)
+        if self.identity:
+            y = ops.moe_identity(y, ident, x)
+        return y if self.float32_out else ops.stream_sum(None, y, out_dtype=x.dtype)
 
     def first_weight(self):
         return self.w_gate_up
@@ -173,6 +243,8 @@ class ExpertMixture(FeedForward):
 
     def forward(self, ctx, x):
         x = ops.materialize(x)
+        if self.route == "scored":
+            return self._forward_scored(ctx, x)
         chosen, weights, dense = ops.moe_router(x, self.router, self.top, over_all=self.route == "softmax_renorm", scale=self.scale)
         if (self.per_expert and x.shape[0] >= self.GROUPED_FROM and not getattr(ctx, "all_decode", True)
                 and not torch.cuda.is_current_stream_capturing()):

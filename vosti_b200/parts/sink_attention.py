@@ -21,6 +21,25 @@ of them optional and a parameter of the spec:
   runs earlier in the same step; both have the same kv heads and value width). A source layer's
   checkpoint may carry an unused `vmix`.
 
+* `qkv_bias`: the q, k and v projections have biases (`q.b`, `k.b`, `v.b`), added to the float32
+  products;
+* `head_norm_eps`: every query and key head is divided by its root mean square (eps inside the
+  root) and multiplied by a weight of the head's width shared by all heads (`q.norm`, `k.norm`),
+  before the rotation;
+* a rotation with `interleaved` pairs (2i, 2i + 1) instead of (i, i + rotary_dim / 2);
+* `maps` = 2, differential attention: the q projection holds two queries a head and the k projection
+  two keys a kv head (head by head: map 1, map 2); each map is a softmax attention of its own over
+  the same values, and a head's output is a1 - lambda * a2 with one lambda for the layer,
+  exp(lq1 . lk1) - exp(lq2 . lk2) + `diff` (vectors of the head's width), then divided by its root
+  mean square over the head's values (`out_norm_eps` inside the root, no weight) and multiplied by
+  1 - `diff`;
+* `out_gate`: the concatenated heads are multiplied element by element by sigmoid(W_g x) (`g`), a
+  product of the mixer's own input, before the output projection.
+
+With any of these five the projection (q | k | v | g as one product) stays float32 and one kernel
+(`ops.qkv_heads`) adds the bias, norms, rotates and stores, rounding once; what follows the softmax is
+the attention kernel's last step (`ops.HeadFinish`).
+
 Other parameters: num_heads, num_kv_heads (query head h reads kv head h // (heads / kv_heads)),
 head_dim, v_head_dim, scale, window (0: every earlier key). Keys and values live in the paged
 cache like those of `Attention`, in two tensors of their own widths.
@@ -68,14 +87,31 @@ class SinkAttention(Mixer):
         if self.value_mix not in (None, "source", "mix"):
             raise ConfigError("sink_attention: value_mix is 'source' or 'mix'")
         self.mix = 0.0
+        self.qkv_bias = bool(spec.get("qkv_bias", False))
+        eps = spec.get("head_norm_eps")
+        self.head_norm_eps = None if eps is None else float(eps)
+        self.maps = int(spec.get("maps", 1) or 1)
+        self.diff = float(spec.get("diff", 0.0) or 0.0)
+        self.out_norm_eps = float(spec.get("out_norm_eps", 0.0) or 0.0)
+        self.out_gate = bool(spec.get("out_gate", False))
+        self.lam = 0.0
+        self.b_qkv = self.q_norm = self.k_norm = None
+        if self.maps not in (1, 2):
+            raise ConfigError("sink_attention: a head has one score map or two")
         self.rotation = build_position(spec.get("position"), hidden_size, self.dk)
         self.freq, self.magnitude = None, 1.0
         if self.has_sink and self.sink_value is not None:
             raise ConfigError("sink_attention: a learned sink or a constant one, not both")
         if self.chunk < 0 or (self.chunk and self.window):
             raise ConfigError("sink_attention: a window or a chunk, not both, and neither negative")
-        if self.rotation is not None and (not hasattr(self.rotation, "frequencies") or self.rotation.interleaved):
-            raise ConfigError("sink_attention: the rotation must give frequencies and pair element i with i + rotary_dim / 2")
+        if self.rotation is not None and not hasattr(self.rotation, "frequencies"):
+            raise ConfigError("sink_attention: the rotation must give frequencies")
+        # the plain path (qkv_store) or the one with bias, head norms, maps, neighbouring pairs or a gate (qkv_heads)
+        self.by_heads = (self.qkv_bias or self.head_norm_eps is not None or self.maps > 1 or self.out_gate
+                         or (self.rotation is not None and self.rotation.interleaved))
+        if self.by_heads and (self.temp_coef or self.value_mix is not None):
+            raise ConfigError("sink_attention: a query temperature or value mixing does not go with bias, head norms, "
+                              "maps, neighbouring pairs or an output gate")
         if self.nq <= 0 or self.nkv <= 0 or self.nq % self.nkv:
             raise ConfigError(f"sink_attention: num_heads {self.nq} must be a positive multiple of num_kv_heads {self.nkv}")
         if not 0 < self.dk <= 256 or not 0 < self.dv <= 256:
@@ -88,8 +124,18 @@ class SinkAttention(Mixer):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         h, nq, nkv, dk, dv = self.hidden_size, self.nq, self.nkv, self.dk, self.dv
-        specs = {"q": WeightSpec((nq * dk, h)), "k": WeightSpec((nkv * dk, h)), "v": WeightSpec((nkv * dv, h)),
+        m = self.maps
+        specs = {"q": WeightSpec((nq * m * dk, h)), "k": WeightSpec((nkv * m * dk, h)), "v": WeightSpec((nkv * dv, h)),
                  "o": WeightSpec((h, nq * dv))}
+        if self.qkv_bias:
+            specs.update({"q.b": WeightSpec((nq * m * dk,), std=0.1), "k.b": WeightSpec((nkv * m * dk,), std=0.1),
+                          "v.b": WeightSpec((nkv * dv,), std=0.1)})
+        if self.head_norm_eps is not None:
+            specs.update({"q.norm": WeightSpec((dk,), init="norm", std=0.1), "k.norm": WeightSpec((dk,), init="norm", std=0.1)})
+        if m == 2:
+            specs.update({name: WeightSpec((dk,), std=0.1) for name in ("lq1", "lk1", "lq2", "lk2")})
+        if self.out_gate:
+            specs["g"] = WeightSpec((nq * dv, h))
         if self.bias_rows:
             specs["rel"] = WeightSpec((self.bias_rows, nq), std=1.0)
         if self.has_sink:
@@ -99,7 +145,15 @@ class SinkAttention(Mixer):
         return specs
 
     def load(self, tensors, dtype):
-        parts = [tensors["q"], tensors["k"], tensors["v"]]
+        parts = [tensors["q"], tensors["k"], tensors["v"]] + ([tensors["g"]] if self.out_gate else [])
+        if self.qkv_bias:
+            self.b_qkv = torch.cat([tensors[name].float() for name in ("q.b", "k.b", "v.b")]).contiguous()
+        if self.head_norm_eps is not None:
+            self.q_norm, self.k_norm = tensors["q.norm"].float().contiguous(), tensors["k.norm"].float().contiguous()
+        if self.maps == 2:
+            # one number for the layer, formed in float32
+            lq1, lk1, lq2, lk2 = (tensors[name].float() for name in ("lq1", "lk1", "lq2", "lk2"))
+            self.lam = float((torch.exp((lq1 * lk1).sum()) - torch.exp((lq2 * lk2).sum())).item()) + self.diff
         common = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
         self.w_qkv = prepare_weight(torch.cat([p.to(common) for p in parts], dim=0).contiguous(), dtype)
         self.w_o = prepare_weight(tensors["o"], dtype)
@@ -129,10 +183,32 @@ class SinkAttention(Mixer):
         return self.w_qkv
 
     def cache_spec(self) -> PagedCacheSpec:
-        return PagedCacheSpec(entries=2, heads=self.nkv, width=self.dk, window=self.window, widths=(self.dk, self.dv))
+        # with maps, a kv head's entry holds its keys of all maps side by side
+        return PagedCacheSpec(entries=2, heads=self.nkv, width=self.maps * self.dk, window=self.window,
+                              widths=(self.maps * self.dk, self.dv))
+
+    def _forward_by_heads(self, ctx, x, cache, writes_cache, group):
+        proj = linear(ctx, x, self.w_qkv, out_dtype=torch.float32)
+        rotation = self.rotation
+        q = ops.qkv_heads(proj, cache.k if writes_cache else None, cache.v if writes_cache else None, nq=self.nq, nkv=self.nkv,
+                          maps=self.maps, dk=self.dk, dv=self.dv, page_size=group.page_size, positions=ctx.positions,
+                          slot_mapping=group.slot_mapping, out_dtype=ctx.dtype, status=ctx.status, bias=self.b_qkv,
+                          q_norm=self.q_norm, k_norm=self.k_norm, eps=self.head_norm_eps or 0.0, freq=self.freq,
+                          interleaved=bool(rotation is not None and rotation.interleaved), magnitude=self.magnitude)
+        finish = None
+        if self.maps == 2 or self.out_gate:
+            width = (self.nq + self.nkv) * self.maps * self.dk + self.nkv * self.dv
+            finish = ops.HeadFinish(lam=self.lam, unit_norm=self.maps == 2, eps=self.out_norm_eps, out_scale=1.0 - self.diff,
+                                    gate=proj[:, width:] if self.out_gate else None)
+        attn = ops.attention_sink(ctx, q, cache.k, cache.v, group, nq=self.nq, nkv=self.nkv, dk=self.dk, dv=self.dv,
+                                  scale=self.scale, window=self.window, bias=self.bias_table, sink=self.sink, chunk=self.chunk,
+                                  maps=self.maps, finish=finish)
+        return linear(ctx, attn, self.w_o, out_dtype=torch.float32)
 
     def forward(self, ctx, x, cache, writes_cache: bool = True):
         group = ctx.group(cache.group)
+        if self.by_heads:
+            return self._forward_by_heads(ctx, x, cache, writes_cache, group)
         qkv = ops.materialize(linear(ctx, x, self.w_qkv))
         v_source = None
         if self.value_mix == "source":
