@@ -173,7 +173,7 @@ def forward(config, weights, tokens, dtype=torch.float64, streams=None):
     """Logits [T, vocab] of one sequence; `streams` (a list) receives the stream after every layer."""
     weights = {k: v.to(dtype) for k, v in weights.items()}
     eps, alpha = float(config["norm"]["eps"]), float(config["postln_alpha"])
-    x = weights["embed"][torch.as_tensor(tokens, dtype=torch.long)] * float(config["embedding"]["scale"])
+    x = weights["embed"][torch.as_tensor(tokens, dtype=torch.long)] * float((config.get("embedding") or {}).get("scale", 1.0))
     for i, entry in enumerate(config["layers"]):
         x = layer(x, weights, i, entry, eps, alpha)
         if streams is not None:
