@@ -38,6 +38,10 @@ model, at the same sizes.
 sublayer over a float32 stream: latent attention, windowed attention with value mixing and a
 selective scan in turn, dense feed-forwards) beside Mugizen with dense feed-forwards at the
 same sizes (`--design-sizes s,m`).
+`--design nefipel` does the same for the Nefipel design (post-norm layers over a float32 stream,
+gated attention and differential attention in turn, dense feed-forwards or, with size moe,
+experts chosen by corrected scores with identity experts and a shared expert) beside Qwen3
+(beside Mugizen where there are experts).
 """
 from __future__ import annotations
 
@@ -449,12 +453,52 @@ def beralix_flops(size, tokens):
     return 2.0 * tokens * per_token + 2.0 * V * W + scores
 
 
+def nefipel_config(size):
+    """A Nefipel config.json of these sizes: gated attention (heads of 128, half of each head rotated)
+    and differential attention (two maps of 64 a head over values of 128, whole-map rescaled
+    rotation) in turn. Feed-forwards are dense, or with size "moe" the differential layers have the
+    size's experts (two of them chosen, among the experts and two identity experts in two groups of
+    which one is kept) and a shared expert as wide as one expert."""
+    H, G, W = size["heads"], size["kv"], size["width"]
+    yarn = dict(factor=8.0, original=4096, fast=32.0, slow=1.0)
+    dense = dict(kind="dense", ff=size["ff"])
+    sparse = dense
+    if size["moe"]:
+        m = size["moe"]
+        sparse = dict(kind="moe", expert=dict(ff=m["ff"]), shared=dict(ff=m["ff"]),
+                      router=dict(experts=m["experts"], top=m["top"], identity=2, groups=dict(count=2, keep=1)))
+    gated = dict(type="attention", mlp=dense, mixer=dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5,
+                                                         rot=dict(base=10000.0, dims=64)))
+    diff = dict(type="attention_2", mlp=sparse, mixer=dict(heads=H, kv_heads=G, dim=64, vdim=128, scale=64 ** -0.5, diff=0.3,
+                                                           rot=dict(base=500000.0, dims=64, scaling=yarn)))
+    return dict(architecture="Nefipel", vocab=size["vocab"], width=W, norm=dict(eps=1e-5), postln_alpha=2.0,
+                embedding=dict(scale=W ** 0.5), layers=[(gated, diff)[i % 2] for i in range(size["layers"])])
+
+
+def nefipel_flops(size, tokens):
+    """Multiply-add work of one prompt, times two, for `nefipel_config(size)`: products (of the experts,
+    those a token chooses and the shared one) and both maps' scores and weighted sums."""
+    W, H, G, F, L, V = size["width"], size["heads"], size["kv"], size["ff"], size["layers"], size["vocab"]
+    gated = W * (H + 2 * G) * 128 + W * H * 128 + H * 128 * W             # q | k | v, the gate, the output
+    diff = W * (2 * H * 64 + 2 * G * 64 + G * 128) + H * 128 * W
+    sparse = 3 * W * F
+    if size["moe"]:
+        m = size["moe"]
+        sparse = 2 * W * m["ff"] * (m["top"] + 1) + W * (m["experts"] + 3)
+    per_token = sum((gated + 3 * W * F) if i % 2 == 0 else (diff + sparse) for i in range(L))
+    pairs = tokens * (tokens + 1) / 2
+    scores = sum(H * (128 * 4.0 if i % 2 == 0 else (2 * 64 + 2 * 128) * 2.0) * pairs for i in range(L))
+    return 2.0 * tokens * per_token + 2.0 * V * W + scores
+
+
 def design_flops(size, tokens, design):
     """Multiply-add work of one prompt of `tokens` tokens, times two: the products and the attention."""
     if design == "vivesun":
         return vivesun_flops(size, tokens)
     if design == "beralix":
         return beralix_flops(size, tokens)
+    if design == "nefipel":
+        return nefipel_flops(size, tokens)
     W, H, G, F, L, V = size["width"], size["heads"], size["kv"], size["ff"], size["layers"], size["vocab"]
     d = 128
     attention = W * (H + 2 * G) * d + H * d * W
@@ -484,6 +528,8 @@ def design_engine(kind, size, max_batch):
         spec = model_spec_from_config(config, shapes)
     elif kind == "beralix":
         spec = model_spec_from_config(beralix_config(size))
+    elif kind == "nefipel":
+        spec = model_spec_from_config(nefipel_config(size))
     else:
         spec = model_spec_from_config(qwen3(size["layers"], size["width"], size["heads"], size["kv"], size["ff"],
                                             context=CONTEXT + 2048) | {"vocab_size": size["vocab"]})
@@ -528,7 +574,7 @@ def design_one(args, name, kind) -> dict:
     return entry
 
 
-BESIDE = {"mugizen": "qwen3", "vivesun": "mugizen", "beralix": "mugizen"}      # the engine's closest other model
+BESIDE = {"mugizen": "qwen3", "vivesun": "mugizen", "beralix": "mugizen", "nefipel": "qwen3"}      # the engine's closest other model
 
 
 def design_main(args) -> int:
@@ -549,7 +595,9 @@ def design_main(args) -> int:
         row = {}
         for kind in (args.design, BESIDE[args.design]):
             if kind == "qwen3" and size["moe"]:
-                continue                      # the engine has no other model with experts to stand beside
+                if args.design != "nefipel":
+                    continue                  # the engine has no other model with experts to stand beside
+                kind = "mugizen"              # Nefipel's experts stand beside Mugizen's
             child = subprocess.run([sys.executable, os.path.abspath(__file__), "--design", args.design, "--design-one",
                                     f"{name}:{kind}", "--steps", str(args.steps), "--warmup", str(args.warmup),
                                     "--context", str(CONTEXT), "--page", str(PAGE)],
@@ -587,7 +635,7 @@ def main() -> int:
                         help="read every step's tokens before the next step is planned (default: the engine's async scheduling)")
     parser.add_argument("--batch-invariant", default="off", choices=["off", "decode", "full"],
                         help="measure with the engine's bitwise-invariance modes (the default run has them off)")
-    parser.add_argument("--design", default="", choices=["", "mugizen", "vivesun", "beralix"],
+    parser.add_argument("--design", default="", choices=["", "mugizen", "vivesun", "beralix", "nefipel"],
                         help="measure this design beside the engine's closest other model at equal layer sizes instead of the headline")
     parser.add_argument("--design-sizes", default="s,m,moe", help="which of the sizes s, m, moe (comma-separated)")
     parser.add_argument("--design-one", default="", help=argparse.SUPPRESS)      # size:design, one model in this process

@@ -140,7 +140,8 @@ def test_gated_attention_mixer_against_plain(dtype, heads, kv, dk, dv, dims, sca
 @pytest.mark.parametrize("heads,kv,dk,dv,dims,scaling,diff,page", [
     (3, 1, 10, 14, 6, YARN, 0.2, 8), (2, 2, 20, 8, 20, None, 0.45, 8), (1, 1, 2, 3, 2, YARN, 0.1, 4), (4, 2, 64, 64, 64, YARN, 0.3, 16),
     (2, 1, 32, 96, 16, None, 0.25, 16), (8, 2, 48, 96, 48, dict(factor=4.0, original=64, fast=16.0, slow=2.0), 0.7, 8),
-    (2, 1, 128, 256, 64, None, 0.5, 16)])
+    (2, 1, 128, 256, 64, None, 0.5, 16), (4, 2, 64, 128, 64, YARN, 0.3, 16), (2, 1, 128, 64, 32, None, 0.2, 16), (6, 2, 128, 128, 128, None, 0.4, 32),
+    (2, 2, 64, 64, 16, None, 0.3, 8)])
 def test_differential_attention_mixer_against_plain(dtype, heads, kv, dk, dv, dims, scaling, diff, page):
     gen = torch.Generator().manual_seed(heads * 100 + dk + 1)
     width, T, eps = 72, 150, 1e-5
@@ -151,6 +152,9 @@ def test_differential_attention_mixer_against_plain(dtype, heads, kv, dk, dv, di
     W = weights_of(mixer, gen)
     give(mixer, W, dtype)
     assert mixer.lam == pytest.approx(plain.differential_lambda({k: v.double() for k, v in W.items()}, diff), rel=1e-5)
+    # in bfloat16 the maps run as heads of their own where the tensor-core kernels take the wider of the two widths
+    assert mixer.expanded == (max(dk, dv) if dtype == torch.bfloat16 and max(dk, dv) in (64, 128) else 0)
+    assert mixer.cache_spec().heads == (2 * kv if mixer.expanded else kv)
     x = rounded(T, width, gen=gen)
     want = plain.differential_attention(x.double(), {k: v.double() for k, v in W.items()}, block, eps).float()
     for sizes in CUTS(T):
@@ -221,6 +225,20 @@ def test_projection_post_pass_alone():
         v_got = v_cache.permute(0, 2, 1, 3).reshape(pages * page, nkv, dv)[:T].cpu()
         assert torch.allclose(k_got, k.float(), atol=2e-5, rtol=2e-5)
         assert torch.allclose(v_got, v.float(), atol=2e-5, rtol=2e-5)
+        # every map a head of its own, D wide: zeros after a head's own elements, a kv head's values once per map
+        D = max(dk, dv) + 8
+        k_wide = torch.full((pages, nkv * maps, page, D), 7.0, device=DEV)
+        v_wide = torch.full((pages, nkv * maps, page, D), 7.0, device=DEV)
+        wide = ops.qkv_heads(proj.to(DEV), k_wide, v_wide, nq=nq, nkv=nkv, maps=maps, dk=dk, dv=dv, page_size=page,
+                             positions=pos.to(DEV, torch.int32), slot_mapping=slots, out_dtype=torch.float32, status=status,
+                             bias=bias.to(DEV), q_norm=qn.to(DEV), k_norm=kn.to(DEV), eps=eps,
+                             freq=torch.tensor(freqs, dtype=torch.float32, device=DEV), interleaved=interleaved, magnitude=magnitude,
+                             expanded_width=D).cpu().view(T, nq * maps, D)
+        assert torch.equal(wide[..., :dk], got.cpu().view(T, nq * maps, dk)) and not wide[..., dk:].any()
+        k_rows = k_wide.permute(0, 2, 1, 3).reshape(pages * page, nkv * maps, D)[:T].cpu()
+        v_rows = v_wide.permute(0, 2, 1, 3).reshape(pages * page, nkv, maps, D)[:T].cpu()
+        assert torch.equal(k_rows[..., :dk], k_got) and not k_rows[..., dk:].any()
+        assert all(torch.equal(v_rows[:, :, m, :dv], v_got) for m in range(maps)) and not v_rows[..., dv:].any()
 
 
 # ---------------------------------------------------------------- feed-forwards

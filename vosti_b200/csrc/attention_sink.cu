@@ -224,26 +224,31 @@ __device__ __forceinline__ void finish_head(const float (&acc)[MAPS][MAX_W / 32]
   }
 }
 
-// The same on attention outputs another kernel wrote: a [tokens, nq, MAPS, dv] -> out [tokens, nq, dv].
+// The same on attention outputs another kernel wrote: a [tokens, nq * MAPS, a_width] -> out [tokens, nq, dv],
+// of a's rows the first dv elements. pair_group 0: head h's maps are rows h * MAPS + m; pair_group r > 0
+// (maps that ran as heads of their own, grouped by kv head): rows h + (h / r) * r + m * r.
 template <typename T, int MAPS>
 __global__ void __launch_bounds__(WARPS * 32)
-head_finish_kernel(const T* __restrict__ a, T* __restrict__ out, int tokens, int nq, int dv, HeadFinish f) {
+head_finish_kernel(const T* __restrict__ a, T* __restrict__ out, int tokens, int nq, int dv, int a_width, int pair_group,
+                   HeadFinish f) {
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t wid = (int64_t)blockIdx.x * WARPS + warp;
   if (wid >= (int64_t)tokens * nq) return;
+  const int t = (int)(wid / nq), h = (int)(wid % nq);
   float acc[MAPS][MAX_W / 32], inv[MAPS];
 #pragma unroll
   for (int m = 0; m < MAPS; ++m) {
     inv[m] = 1.f;
+    const int64_t row = (int64_t)t * nq * MAPS + (pair_group > 0 ? h + (h / pair_group) * pair_group + m * pair_group : h * MAPS + m);
 #pragma unroll
     for (int i = 0; i < MAX_W / 32; ++i) {
       const int idx = lane + 32 * i;
-      acc[m][i] = idx < dv ? to_f32(a[(wid * MAPS + m) * dv + idx]) : 0.f;
+      acc[m][i] = idx < dv ? to_f32(a[row * a_width + idx]) : 0.f;
     }
   }
-  finish_head<T, MAPS>(acc, inv, f, (int)(wid / nq), (int)(wid % nq), dv, out + wid * dv);
+  finish_head<T, MAPS>(acc, inv, f, t, h, dv, out + wid * dv);
 }
 
 // After a q | k | v projection (float32 or the serving type, rows `proj_stride` elements apart so that
@@ -254,13 +259,18 @@ head_finish_kernel(const T* __restrict__ a, T* __restrict__ out, int tokens, int
 // [tokens, nq * maps * dk], keys and values to their cache slots. With `maps` score maps a head the
 // projection holds nq * maps query heads and nkv * maps key heads, head by head, and the key cache's
 // entry of a kv head is its maps keys side by side: [pages, nkv, page_size, maps * dk].
+// `expanded`: every map is a head of its own for kernels that know one map a head and one width:
+// queries go out dk_out wide (zeros after the first dk elements), the caches are
+// [pages, nkv * maps, page_size, dk_out | dv_out], key head number kv * maps + m, a kv head's values
+// written once for each of its maps, zeros after the first dk (dv) elements.
 template <typename T>
 __global__ void __launch_bounds__(256)
 qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_stride, const float* __restrict__ bias,
                  T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ positions,
                  const int* __restrict__ slot_mapping, int64_t num_slots, int page_size, int nq, int nkv, int maps, int dk, int dv,
                  const void* __restrict__ q_norm, const void* __restrict__ k_norm, int norm_f32, float eps,
-                 const float* __restrict__ freq, int rot_half, int interleaved, float magnitude, unsigned* status) {
+                 const float* __restrict__ freq, int rot_half, int interleaved, float magnitude, int expanded, int dk_out,
+                 int dv_out, unsigned* status) {
   extern __shared__ float heads_smem[];          // [2 * rot_half] cosines and sines, then [warps][dk] a head per warp
   pdl_wait();
   pdl_launch_dependents();
@@ -295,6 +305,17 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
       if (!store) continue;
       const int g = hd - nqm - nkm;
       const int64_t off = wq + wk + (int64_t)g * dv;
+      if (expanded) {
+        for (int i = lane; i < dv_out; i += 32) {
+          float x = 0.f;
+          if (i < dv) {
+            x = load_flex(proj, proj_f32, row + off + i);
+            if (bias != nullptr) x += bias[off + i];
+          }
+          for (int c = 0; c < maps; ++c) v_cache[((page * nkm + g * maps + c) * page_size + offset) * dv_out + i] = from_f32<T>(x);
+        }
+        continue;
+      }
       T* dst = v_cache + ((page * nkv + g) * page_size + offset) * dv;
       for (int i = lane; i < dv; i += 32) {
         float x = load_flex(proj, proj_f32, row + off + i);
@@ -329,11 +350,14 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
     }
     T* dst;
     if (is_q) {
-      dst = q_out + (int64_t)t * wq + off;
+      dst = expanded ? q_out + ((int64_t)t * nqm + hd) * dk_out : q_out + (int64_t)t * wq + off;
     } else {
       const int kh = hd - nqm, g = kh / maps, m = kh % maps;
-      dst = k_cache + (((page * nkv + g) * page_size + offset) * maps + m) * dk;
+      dst = expanded ? k_cache + ((page * nkm + kh) * page_size + offset) * dk_out
+                     : k_cache + (((page * nkv + g) * page_size + offset) * maps + m) * dk;
     }
+    if (expanded)
+      for (int i = dk + lane; i < dk_out; i += 32) dst[i] = from_f32<T>(0.f);
     if (rot_half > 0) {
 #pragma unroll
       for (int j = 0; j < MAX_W / 32; ++j)
@@ -646,20 +670,22 @@ VOSTI_API int vosti_attention_sink(const void* q, const void* k_cache, const voi
 }
 
 // a: [tokens, nq, maps, dv] attention outputs -> out [tokens, nq, dv] (see HeadFinish).
-VOSTI_API int vosti_head_finish(const void* a, void* out, int tokens, int nq, int maps, int dv, float lambda, int unit_norm, float eps,
+VOSTI_API int vosti_head_finish(const void* a, void* out, int tokens, int nq, int maps, int dv, int a_width, int pair_group,
+                                float lambda, int unit_norm, float eps,
                                 float out_scale, const void* gate, int gate_f32, long long gate_stride, int is_f32,
                                 cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && nq > 0 && dv > 0 && dv <= MAX_W && (maps == 1 || maps == 2), "head_finish: bad sizes");
+  VOSTI_REQUIRE(a_width >= dv && pair_group >= 0 && (pair_group == 0 || nq % pair_group == 0), "head_finish: bad input layout");
   VOSTI_REQUIRE(gate == nullptr || gate_stride >= (long long)nq * dv, "head_finish: the gate's rows are narrower than the heads");
   if (tokens == 0) return VOSTI_OK;
   const HeadFinish f = {lambda, out_scale, eps, unit_norm, gate, gate_f32, gate_stride};
   const unsigned blocks = (unsigned)(((int64_t)tokens * nq + WARPS - 1) / WARPS);
   if (is_f32) {
-    if (maps == 2) vosti_launch(head_finish_kernel<float, 2>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const float*)a, (float*)out, tokens, nq, dv, f);
-    else vosti_launch(head_finish_kernel<float, 1>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const float*)a, (float*)out, tokens, nq, dv, f);
+    if (maps == 2) vosti_launch(head_finish_kernel<float, 2>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const float*)a, (float*)out, tokens, nq, dv, a_width, pair_group, f);
+    else vosti_launch(head_finish_kernel<float, 1>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const float*)a, (float*)out, tokens, nq, dv, a_width, pair_group, f);
   } else {
-    if (maps == 2) vosti_launch(head_finish_kernel<bf16, 2>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const bf16*)a, (bf16*)out, tokens, nq, dv, f);
-    else vosti_launch(head_finish_kernel<bf16, 1>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const bf16*)a, (bf16*)out, tokens, nq, dv, f);
+    if (maps == 2) vosti_launch(head_finish_kernel<bf16, 2>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const bf16*)a, (bf16*)out, tokens, nq, dv, a_width, pair_group, f);
+    else vosti_launch(head_finish_kernel<bf16, 1>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const bf16*)a, (bf16*)out, tokens, nq, dv, a_width, pair_group, f);
   }
   VOSTI_LAUNCH_CHECK();
 }
@@ -667,12 +693,14 @@ VOSTI_API int vosti_head_finish(const void* a, void* out, int tokens, int nq, in
 // proj: [tokens, >= (nq * maps + nkv * maps) * dk + nkv * dv] float32 or bfloat16, rows proj_stride elements apart; bias float32
 // over the q | k | v columns, or null; q_norm / k_norm [dk] (float32 or bfloat16, both of one type), or null;
 // freq float32 [rot_half], or rot_half 0. Outputs in the serving type: q_out [tokens, nq * maps * dk];
-// caches [pages, nkv, page_size, maps * dk | dv] (null: queries only).
+// caches [pages, nkv, page_size, maps * dk | dv] (null: queries only). `expanded` (see the kernel): q_out
+// [tokens, nq * maps * dk_out], caches [pages, nkv * maps, page_size, dk_out | dv_out].
 VOSTI_API int vosti_qkv_heads(const void* proj, int proj_f32, long long proj_stride, const float* bias, void* q_out, void* k_cache,
                               void* v_cache, const int* positions, const int* slot_mapping, int64_t num_slots, int page_size,
                               int tokens, int nq, int nkv, int maps, int dk, int dv, const void* q_norm, const void* k_norm,
                               int norm_f32, float eps, const float* freq, int rot_half, int interleaved, float magnitude,
-                              int is_f32, unsigned* status, cudaStream_t stream) {
+                              int expanded, int dk_out, int dv_out, int is_f32, unsigned* status, cudaStream_t stream) {
+  VOSTI_REQUIRE(!expanded || (dk_out >= dk && dv_out >= dv), "qkv_heads: expanded heads are at least as wide as the heads");
   VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv >= 0 && maps >= 1 && dk > 0 && dv > 0 && dk <= MAX_W && dv <= MAX_W, "qkv_heads: bad sizes");
   VOSTI_REQUIRE(proj_stride >= (long long)(nq + nkv) * maps * dk + (long long)nkv * dv, "qkv_heads: the projection's rows are too narrow");
   VOSTI_REQUIRE(k_cache == nullptr || (v_cache != nullptr && slot_mapping != nullptr && page_size > 0), "qkv_heads: a cache needs slots");
@@ -684,10 +712,10 @@ VOSTI_API int vosti_qkv_heads(const void* proj, int proj_f32, long long proj_str
   if (is_f32)
     vosti_launch(qkv_heads_kernel<float>, dim3(tokens), dim3(threads), smem, stream, proj, proj_f32, (int64_t)proj_stride, bias, (float*)q_out,
                  (float*)k_cache, (float*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, maps, dk, dv, q_norm, k_norm,
-                 norm_f32, eps, freq, rot_half, interleaved, magnitude, status);
+                 norm_f32, eps, freq, rot_half, interleaved, magnitude, expanded, dk_out, dv_out, status);
   else
     vosti_launch(qkv_heads_kernel<bf16>, dim3(tokens), dim3(threads), smem, stream, proj, proj_f32, (int64_t)proj_stride, bias, (bf16*)q_out,
                  (bf16*)k_cache, (bf16*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, maps, dk, dv, q_norm, k_norm,
-                 norm_f32, eps, freq, rot_half, interleaved, magnitude, status);
+                 norm_f32, eps, freq, rot_half, interleaved, magnitude, expanded, dk_out, dv_out, status);
   VOSTI_LAUNCH_CHECK();
 }

@@ -917,15 +917,20 @@ class HeadFinish:
 _NO_FINISH = HeadFinish()
 
 
-def head_finish(a: torch.Tensor, finish: "HeadFinish", *, nq: int, maps: int, dv: int) -> torch.Tensor:
-    """`finish` applied to attention outputs a [tokens, nq * maps * dv] that another kernel wrote;
-    returns [tokens, nq * dv]."""
+def head_finish(a: torch.Tensor, finish: "HeadFinish", *, nq: int, maps: int, dv: int, in_width: Optional[int] = None,
+                pair_group: int = 0) -> torch.Tensor:
+    """`finish` applied to attention outputs that another kernel wrote, a [tokens, nq * maps * in_width]
+    (of every row of `in_width` elements, default dv, the first dv count); returns [tokens, nq * dv].
+    `pair_group` 0: head h's maps are rows h * maps + m of a token; r > 0 (maps that ran as heads of
+    their own, grouped by kv head with r heads a kv head): rows h + (h // r) * r + m * r."""
     _contig(a)
     tokens = a.shape[0]
-    if a.shape[1] != nq * maps * dv:
+    in_width = dv if in_width is None else in_width
+    if a.shape[1] != nq * maps * in_width:
         raise KernelError("head_finish: the input's width does not match heads, maps and width")
     out = torch.empty((tokens, nq * dv), dtype=a.dtype, device=a.device)
-    _check(library().vosti_head_finish(_p(a), _p(out), tokens, nq, maps, dv, *finish.args(), _is_f32(a), _stream()), "head_finish")
+    _check(library().vosti_head_finish(_p(a), _p(out), tokens, nq, maps, dv, in_width, pair_group, *finish.args(), _is_f32(a),
+                                       _stream()), "head_finish")
     return out
 
 
@@ -933,7 +938,8 @@ def qkv_heads(proj: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Opti
               maps: int = 1, dk: int, dv: int, page_size: int, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
               out_dtype: torch.dtype, status: torch.Tensor, bias: Optional[torch.Tensor] = None,
               q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None, eps: float = 0.0,
-              freq: Optional[torch.Tensor] = None, interleaved: bool = False, magnitude: float = 1.0) -> torch.Tensor:
+              freq: Optional[torch.Tensor] = None, interleaved: bool = False, magnitude: float = 1.0,
+              expanded_width: int = 0) -> torch.Tensor:
     """After a q | k | v projection `proj` [tokens, >= (nq + nkv) * maps * dk + nkv * dv] (float32 or the
     serving type; further columns may follow): `bias` (float32, over the q | k | v columns) is
     added; every query and key head is RMS-normed with the weights `q_norm` / `k_norm` [dk] shared
@@ -942,7 +948,10 @@ def qkv_heads(proj: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Opti
     `magnitude`); all in float32, rounded once to `out_dtype`. The queries are returned
     [tokens, nq * maps * dk]; keys and values go to their cache slots ([pages, nkv, page_size,
     maps * dk] and [pages, nkv, page_size, dv]). `maps` > 1: the projection holds `maps` query heads
-    a head and `maps` key heads a kv head, head by head."""
+    a head and `maps` key heads a kv head, head by head. `expanded_width` D > 0 lays every map out as
+    a head of its own, D wide, for kernels that know one map a head and one width: queries
+    [tokens, nq * maps * D] and caches [pages, nkv * maps, page_size, D] with zeros after a head's own
+    elements, a kv head's values stored once for each of its maps."""
     proj = materialize(proj)
     _contig(k_cache, v_cache, positions, slot_mapping, freq, bias, q_norm, k_norm)
     tokens = proj.shape[0]
@@ -961,13 +970,16 @@ def qkv_heads(proj: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Opti
     for cache in (k_cache, v_cache):
         if cache is not None and cache.dtype != out_dtype:
             raise KernelError("qkv_heads: the caches hold the output type")
-    q = torch.empty((tokens, nq * maps * dk), dtype=out_dtype, device=proj.device)
-    num_slots = 0 if k_cache is None else k_cache.numel() // (nkv * maps * dk)
+    D = int(expanded_width)
+    if D and (D < dk or D < dv):
+        raise KernelError("qkv_heads: expanded heads are at least as wide as the key and value heads")
+    q = torch.empty((tokens, nq * maps * (D or dk)), dtype=out_dtype, device=proj.device)
+    num_slots = 0 if k_cache is None else k_cache.numel() // (nkv * maps * (D or dk))
     _check(library().vosti_qkv_heads(_p(proj), _is_f32(proj), ctypes.c_longlong(proj.stride(0)), _p(bias), _p(q), _p(k_cache),
                                      _p(v_cache), _p(positions), _p(slot_mapping), ctypes.c_int64(num_slots), page_size, tokens,
                                      nq, nkv, maps, dk, dv, _p(q_norm), _p(k_norm), norm_flag, ctypes.c_float(eps), _p(freq),
                                      0 if freq is None else freq.shape[0], int(bool(interleaved)), ctypes.c_float(magnitude),
-                                     1 if out_dtype == torch.float32 else 0, _p(status), _stream()), "qkv_heads")
+                                     int(D > 0), D, D, 1 if out_dtype == torch.float32 else 0, _p(status), _stream()), "qkv_heads")
     return q
 
 
@@ -1043,6 +1055,12 @@ def attention_sink(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     if finish is not None:
         return head_finish(out, finish, nq=nq, maps=1, dv=dv)
     return out
+
+
+def attention_heads_supported(dtype: torch.dtype, width: int, group: int) -> bool:
+    """Whether heads of equal key and value width `width` with `group` query heads a kv head can run on
+    the tensor-core attention kernels (given pages of a multiple of 16 tokens)."""
+    return bool(dtype == torch.bfloat16 and group <= 16 and library().vosti_attention_prefill_tc_supported(width, 16))
 
 
 # ---------------------------------------------------------------- layer norm over the stream

@@ -36,6 +36,13 @@ of them optional and a parameter of the spec:
 * `out_gate`: the concatenated heads are multiplied element by element by sigmoid(W_g x) (`g`), a
   product of the mixer's own input, before the output projection.
 
+In bfloat16 serving a layer with two maps whose wider head width (of key and value) is one the
+tensor-core attention kernels take runs every map as a head of its own on those kernels
+("expanded": queries and keys zero-padded to that width, a kv head's values cached once per map,
+the q projection's rows reordered so that the query heads of a key head stand together); the
+maps are combined by a kernel after them. Such a layer's cache holds 2 * maps * kv heads entries
+of that width a token.
+
 With any of these five the projection (q | k | v | g as one product) stays float32 and one kernel
 (`ops.qkv_heads`) adds the bias, norms, rotates and stores, rounding once; what follows the softmax is
 the attention kernel's last step (`ops.HeadFinish`).
@@ -95,6 +102,7 @@ class SinkAttention(Mixer):
         self.out_norm_eps = float(spec.get("out_norm_eps", 0.0) or 0.0)
         self.out_gate = bool(spec.get("out_gate", False))
         self.lam = 0.0
+        self.expanded = 0
         self.b_qkv = self.q_norm = self.k_norm = None
         if self.maps not in (1, 2):
             raise ConfigError("sink_attention: a head has one score map or two")
@@ -145,9 +153,21 @@ class SinkAttention(Mixer):
         return specs
 
     def load(self, tensors, dtype):
-        parts = [tensors["q"], tensors["k"], tensors["v"]] + ([tensors["g"]] if self.out_gate else [])
+        wide = max(self.dk, self.dv)
+        self.expanded = wide if (self.maps > 1 and ops.attention_heads_supported(dtype, wide, self.nq // self.nkv)
+                                 and not self.has_sink and self.sink_value is None and not self.bias_rows) else 0
+        q_rows, q_bias = tensors["q"], tensors.get("q.b")
+        if self.expanded:
+            # query heads in the order (kv head, map, head within the kv head's group)
+            r = self.nq // self.nkv
+            order = torch.tensor([(g * r + j) * self.maps + m for g in range(self.nkv) for m in range(self.maps) for j in range(r)],
+                                 device=q_rows.device)
+            q_rows = q_rows.view(self.nq * self.maps, self.dk, -1)[order].reshape(q_rows.shape)
+            if q_bias is not None:
+                q_bias = q_bias.view(self.nq * self.maps, self.dk)[order].reshape(-1)
+        parts = [q_rows, tensors["k"], tensors["v"]] + ([tensors["g"]] if self.out_gate else [])
         if self.qkv_bias:
-            self.b_qkv = torch.cat([tensors[name].float() for name in ("q.b", "k.b", "v.b")]).contiguous()
+            self.b_qkv = torch.cat([q_bias.float(), tensors["k.b"].float(), tensors["v.b"].float()]).contiguous()
         if self.head_norm_eps is not None:
             self.q_norm, self.k_norm = tensors["q.norm"].float().contiguous(), tensors["k.norm"].float().contiguous()
         if self.maps == 2:
@@ -183,6 +203,8 @@ class SinkAttention(Mixer):
         return self.w_qkv
 
     def cache_spec(self) -> PagedCacheSpec:
+        if getattr(self, "expanded", 0):
+            return PagedCacheSpec(entries=2, heads=self.nkv * self.maps, width=self.expanded, window=self.window)
         # with maps, a kv head's entry holds its keys of all maps side by side
         return PagedCacheSpec(entries=2, heads=self.nkv, width=self.maps * self.dk, window=self.window,
                               widths=(self.maps * self.dk, self.dv))
@@ -194,7 +216,17 @@ class SinkAttention(Mixer):
                           maps=self.maps, dk=self.dk, dv=self.dv, page_size=group.page_size, positions=ctx.positions,
                           slot_mapping=group.slot_mapping, out_dtype=ctx.dtype, status=ctx.status, bias=self.b_qkv,
                           q_norm=self.q_norm, k_norm=self.k_norm, eps=self.head_norm_eps or 0.0, freq=self.freq,
-                          interleaved=bool(rotation is not None and rotation.interleaved), magnitude=self.magnitude)
+                          interleaved=bool(rotation is not None and rotation.interleaved), magnitude=self.magnitude,
+                          expanded_width=self.expanded)
+        if self.expanded:
+            D, m = self.expanded, self.maps
+            each = ops.attention_sink(ctx, q, cache.k, cache.v, group, nq=self.nq * m, nkv=self.nkv * m, dk=D, dv=D,
+                                      scale=self.scale, window=self.window, bias=None, sink=None, chunk=self.chunk)
+            width = (self.nq + self.nkv) * m * self.dk + self.nkv * self.dv
+            finish = ops.HeadFinish(lam=self.lam, unit_norm=True, eps=self.out_norm_eps, out_scale=1.0 - self.diff,
+                                    gate=proj[:, width:] if self.out_gate else None)
+            attn = ops.head_finish(each, finish, nq=self.nq, maps=m, dv=self.dv, in_width=D, pair_group=self.nq // self.nkv)
+            return linear(ctx, attn, self.w_o, out_dtype=torch.float32)
         finish = None
         if self.maps == 2 or self.out_gate:
             width = (self.nq + self.nkv) * self.maps * self.dk + self.nkv * self.dv
