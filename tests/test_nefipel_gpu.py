@@ -370,6 +370,35 @@ def test_whole_prompt_portions_and_decoding_against_plain(models, name, dtype):
         assert close_rows(torch.cat(rows), want, dtype), sizes
 
 
+WIDE = dict(architecture="Nefipel", vocab=512, width=1024, norm=dict(eps=1e-5), postln_alpha=2.0, embedding=dict(scale=32.0), layers=[
+    tiny.gated(8, 2, 128, 128, 0.27, 10000.0, 64, None, tiny.dense(2048)),
+    tiny.differential(8, 2, 64, 128, 0.38, 500000.0, 64, dict(factor=8.0, original=64, fast=32.0, slow=1.0), 0.3,
+                      tiny.moe(4, 2, 512, identity=2, groups=(2, 1), shared=512)),
+    tiny.differential(4, 4, 128, 128, 0.27, 10000.0, 128, None, 0.2, tiny.moe(6, 2, 256)),
+])
+
+
+def test_wide_layers_whose_products_split_their_inner_range(tmp_path):
+    """Layer sizes at which the bfloat16 products of a few tokens split their inner range: the kernels
+    after them (head post-pass, norm after the sum) add the unsummed splits themselves; the dense
+    feed-forward's relu(gate) * up is the product's own last step; both differential layers run their
+    maps as heads of their own. Prompt of a few tokens, then token by token, against the plain form."""
+    assert ops.library().vosti_gemm_tc_splits(1, 1024, 2048) > 1 and ops.library().vosti_gemm_tc_splits(4, 3072, 1024) > 1
+    folder = tiny.write_model(tmp_path / "wide", WIDE, 77)
+    _, W = tiny.tensors_for(WIDE, 77)
+    tokens = prompt(WIDE, 40, 8)
+    want = logits_of(WIDE, W, tokens)
+    for dtype in ("bfloat16", "float32"):
+        runner = ModelRunner(folder, dtype=dtype, num_pages=4, page_size=16, max_requests=2)
+        if dtype == "bfloat16":
+            assert [b.mixer.expanded for b in runner.model.blocks] == [0, 128, 128] and runner.model.blocks[0].feed_forward.fused
+        runner.begin("r")
+        rows = [runner.step([StepEntry("r", tokens[:4], [0, 1, 2, 3])]).cpu()]
+        rows += [runner.step([StepEntry("r", [t], [0])]).cpu() for t in tokens[4:]]
+        runner.check_status()
+        assert close_rows(torch.cat(rows), want, dtype), dtype
+
+
 def test_a_checkpoint_without_the_unused_norm_gives_the_same_logits(models, tmp_path):
     folder, config, W = models["a"]
     bare = tiny.write_model(tmp_path / "bare", config, tiny.ALL["a"][1], unused=False)

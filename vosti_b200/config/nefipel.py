@@ -91,7 +91,7 @@ def _attention(i: int, block: Mapping[str, Any], eps: float, differential: bool)
     common = dict(
         num_heads=_positive_int(block, "heads", where), num_kv_heads=_positive_int(block, "kv_heads", where),
         head_dim=_positive_int(block, "dim", where), v_head_dim=_positive_int(block, "vdim", where),
-        scale=_number(block, "scale", where), window=0, chunk=0, sink=False, head_norm_eps=eps,
+        scale=_number(block, "scale", where), window=0, chunk=0, sink=False, head_norm_eps=eps, partial_out=True,
         position=_rotation(_need(block, "rot", where), where + ".rot", interleaved=differential))
     if differential:
         return PartSpec.make("sink_attention", maps=2, diff=_number(block, "diff", where), out_norm_eps=eps, **common)
@@ -105,7 +105,7 @@ def _feed_forward(i: int, block: Optional[Mapping[str, Any]]) -> Optional[PartSp
     kind = _need(block, "kind", where)
     if kind == "dense":
         return PartSpec.make("swiglu", intermediate_size=_positive_int(block, "ff", where), tensor_names=("gate", "up", "down"),
-                             float32_out=True, activation="relu")
+                             float32_out=True, activation="relu", partial_out=True)
     if kind == "moe":
         router = _need(block, "router", where)
         rw = where + ".router"
@@ -117,7 +117,7 @@ def _feed_forward(i: int, block: Optional[Mapping[str, Any]]) -> Optional[PartSp
             activation="relu2", route="scored", correction=True, identity=_count(router, "identity", rw),
             groups=1 if groups is None else _positive_int(groups, "count", rw + ".groups"),
             keep=1 if groups is None else _positive_int(groups, "keep", rw + ".groups"),
-            shared=0 if shared is None else _positive_int(shared, "ff", where + ".shared"), float32_out=True)
+            shared=0 if shared is None else _positive_int(shared, "ff", where + ".shared"), float32_out=True, partial_out=True)
     raise ConfigError(f"Nefipel config: {where}.kind is {kind!r}; 'dense' and 'moe' are known")
 
 

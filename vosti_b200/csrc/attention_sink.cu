@@ -270,10 +270,18 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
                  const int* __restrict__ slot_mapping, int64_t num_slots, int page_size, int nq, int nkv, int maps, int dk, int dv,
                  const void* __restrict__ q_norm, const void* __restrict__ k_norm, int norm_f32, float eps,
                  const float* __restrict__ freq, int rot_half, int interleaved, float magnitude, int expanded, int dk_out,
-                 int dv_out, unsigned* status) {
+                 int dv_out, int splits, int64_t plane, float* __restrict__ extra_out, int extra_width, unsigned* status) {
+  // splits > 1: proj is float32 [splits, tokens, proj_stride], the unsummed K splits of the product, added in
+  // split order; the columns after q | k | v (extra_width of them: a gate) are then summed into extra_out.
+  // The grid's y cuts a token's heads into pieces of one head a warp.
   extern __shared__ float heads_smem[];          // [2 * rot_half] cosines and sines, then [warps][dk] a head per warp
   pdl_wait();
   pdl_launch_dependents();
+  auto value = [&](int64_t i) {
+    float x = load_flex(proj, proj_f32, i);
+    for (int sp = 1; sp < splits; ++sp) x += reinterpret_cast<const float*>(proj)[sp * plane + i];
+    return x;
+  };
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   float* turn = heads_smem;
   float* buf = heads_smem + 2 * rot_half + warp * dk;
@@ -300,7 +308,14 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
   const int nqm = nq * maps, nkm = nkv * maps;
   const int64_t wq = (int64_t)nqm * dk, wk = (int64_t)nkm * dk;
   const int64_t row = (int64_t)t * proj_stride;
-  for (int hd = warp; hd < nqm + nkm + nkv; hd += nwarps) {
+  const int pieces = extra_out != nullptr ? (extra_width + 255) / 256 : 0;       // the extra columns, 256 a warp
+  for (int hd = blockIdx.y * nwarps + warp; hd < nqm + nkm + nkv + pieces; hd += gridDim.y * nwarps) {
+    if (hd >= nqm + nkm + nkv) {
+      const int64_t off = wq + wk + (int64_t)nkv * dv;
+      const int c0 = (hd - nqm - nkm - nkv) * 256;
+      for (int i = c0 + lane; i < min(c0 + 256, extra_width); i += 32) extra_out[(int64_t)t * extra_width + i] = value(row + off + i);
+      continue;
+    }
     if (hd >= nqm + nkm) {                         // a value head: bias, then its cache slot
       if (!store) continue;
       const int g = hd - nqm - nkm;
@@ -309,7 +324,7 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
         for (int i = lane; i < dv_out; i += 32) {
           float x = 0.f;
           if (i < dv) {
-            x = load_flex(proj, proj_f32, row + off + i);
+            x = value(row + off + i);
             if (bias != nullptr) x += bias[off + i];
           }
           for (int c = 0; c < maps; ++c) v_cache[((page * nkm + g * maps + c) * page_size + offset) * dv_out + i] = from_f32<T>(x);
@@ -318,7 +333,7 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
       }
       T* dst = v_cache + ((page * nkv + g) * page_size + offset) * dv;
       for (int i = lane; i < dv; i += 32) {
-        float x = load_flex(proj, proj_f32, row + off + i);
+        float x = value(row + off + i);
         if (bias != nullptr) x += bias[off + i];
         dst[i] = from_f32<T>(x);
       }
@@ -335,7 +350,7 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
       const int i = lane + 32 * j;
       x[j] = 0.f;
       if (i < dk) {
-        x[j] = load_flex(proj, proj_f32, row + off + i);
+        x[j] = value(row + off + i);
         if (bias != nullptr) x[j] += bias[off + i];
         ss += x[j] * x[j];
       }
@@ -699,8 +714,13 @@ VOSTI_API int vosti_qkv_heads(const void* proj, int proj_f32, long long proj_str
                               void* v_cache, const int* positions, const int* slot_mapping, int64_t num_slots, int page_size,
                               int tokens, int nq, int nkv, int maps, int dk, int dv, const void* q_norm, const void* k_norm,
                               int norm_f32, float eps, const float* freq, int rot_half, int interleaved, float magnitude,
-                              int expanded, int dk_out, int dv_out, int is_f32, unsigned* status, cudaStream_t stream) {
+                              int expanded, int dk_out, int dv_out, int splits, float* extra_out, int extra_width, int is_f32,
+                              unsigned* status, cudaStream_t stream) {
   VOSTI_REQUIRE(!expanded || (dk_out >= dk && dv_out >= dv), "qkv_heads: expanded heads are at least as wide as the heads");
+  VOSTI_REQUIRE(splits >= 1 && (splits == 1 || proj_f32), "qkv_heads: unsummed splits are float32");
+  VOSTI_REQUIRE(extra_out == nullptr || (extra_width > 0 && proj_stride >= (long long)(nq + nkv) * maps * dk + (long long)nkv * dv + extra_width),
+                "qkv_heads: the extra columns lie after q | k | v inside the projection's rows");
+  const int64_t plane = (int64_t)tokens * proj_stride;
   VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv >= 0 && maps >= 1 && dk > 0 && dv > 0 && dk <= MAX_W && dv <= MAX_W, "qkv_heads: bad sizes");
   VOSTI_REQUIRE(proj_stride >= (long long)(nq + nkv) * maps * dk + (long long)nkv * dv, "qkv_heads: the projection's rows are too narrow");
   VOSTI_REQUIRE(k_cache == nullptr || (v_cache != nullptr && slot_mapping != nullptr && page_size > 0), "qkv_heads: a cache needs slots");
@@ -709,13 +729,15 @@ VOSTI_API int vosti_qkv_heads(const void* proj, int proj_f32, long long proj_str
   if (tokens == 0) return VOSTI_OK;
   const int threads = 256;
   const size_t smem = ((size_t)2 * rot_half + (size_t)(threads / 32) * dk) * sizeof(float);
+  const int items = (nq + nkv) * maps + nkv + (extra_out != nullptr ? (extra_width + 255) / 256 : 0);
+  const dim3 grid(tokens, (items + threads / 32 - 1) / (threads / 32));
   if (is_f32)
-    vosti_launch(qkv_heads_kernel<float>, dim3(tokens), dim3(threads), smem, stream, proj, proj_f32, (int64_t)proj_stride, bias, (float*)q_out,
+    vosti_launch(qkv_heads_kernel<float>, grid, dim3(threads), smem, stream, proj, proj_f32, (int64_t)proj_stride, bias, (float*)q_out,
                  (float*)k_cache, (float*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, maps, dk, dv, q_norm, k_norm,
-                 norm_f32, eps, freq, rot_half, interleaved, magnitude, expanded, dk_out, dv_out, status);
+                 norm_f32, eps, freq, rot_half, interleaved, magnitude, expanded, dk_out, dv_out, splits, plane, extra_out, extra_width, status);
   else
-    vosti_launch(qkv_heads_kernel<bf16>, dim3(tokens), dim3(threads), smem, stream, proj, proj_f32, (int64_t)proj_stride, bias, (bf16*)q_out,
+    vosti_launch(qkv_heads_kernel<bf16>, grid, dim3(threads), smem, stream, proj, proj_f32, (int64_t)proj_stride, bias, (bf16*)q_out,
                  (bf16*)k_cache, (bf16*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, maps, dk, dv, q_norm, k_norm,
-                 norm_f32, eps, freq, rot_half, interleaved, magnitude, expanded, dk_out, dv_out, status);
+                 norm_f32, eps, freq, rot_half, interleaved, magnitude, expanded, dk_out, dv_out, splits, plane, extra_out, extra_width, status);
   VOSTI_LAUNCH_CHECK();
 }

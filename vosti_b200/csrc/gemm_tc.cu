@@ -32,7 +32,9 @@ constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int THREADS = 192;
 
-enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
+enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3, EPI_REGLU = 4, EPI_RE2GLU = 5 };
+// Gated epilogues: act(gate) * up with act = SiLU, relu, or the square of relu.
+__host__ __device__ constexpr bool is_gated(int epilogue) { return epilogue == EPI_SWIGLU || epilogue == EPI_REGLU || epilogue == EPI_RE2GLU; }
 
 // Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = bn.
 __host__ __device__ constexpr uint32_t instr_desc(int bn) {
@@ -40,6 +42,11 @@ __host__ __device__ constexpr uint32_t instr_desc(int bn) {
 }
 
 __device__ __forceinline__ float silu(float g) { return g / (1.f + __expf(-g)); }
+__device__ __forceinline__ float gate_act(int epilogue, float g) {
+  if (epilogue == EPI_SWIGLU) return silu(g);
+  const float r = fmaxf(g, 0.f);
+  return epilogue == EPI_RE2GLU ? r * r : r;
+}
 
 // ------------------------------------------------------------------ the kernel
 template <int BN, int STAGES, int KPS>
@@ -170,7 +177,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (epilogue == EPI_SWIGLU) {
+        if (is_gated(epilogue)) {
           // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows
           bf16* y = reinterpret_cast<bf16*>(out);
           const int out_feature = (m0 + quarter * 32) / 2 + (lane & 15);
@@ -180,7 +187,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
             const int t = n0 + c0 + j;
             if (lane < 16 && t < tokens && out_feature < ld_out)
-              y[(int64_t)t * ld_out + out_feature] = __float2bfloat16_rn(silu(mine) * other);
+              y[(int64_t)t * ld_out + out_feature] = __float2bfloat16_rn(gate_act(epilogue, mine) * other);
           }
         } else if (feature < features) {
           if (epilogue == EPI_BF16) {
@@ -220,14 +227,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // into the output: bf16, float32, or SiLU(gate) * up of 16 gate and 16 up columns.
 __device__ __forceinline__ void store_token_columns(const uint32_t (&r)[32], void* __restrict__ out, int token, int f0,
                                                     int features, int ld_out, int epilogue) {
-  if (epilogue == EPI_SWIGLU) {
+  if (is_gated(epilogue)) {
     // columns f0..f0+15 are gate rows, f0+16..f0+31 their up rows (features % 32 == 0)
     bf16* y = reinterpret_cast<bf16*>(out) + (int64_t)token * ld_out + f0 / 2;
     uint32_t packed[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float a = silu(__uint_as_float(r[2 * j])) * __uint_as_float(r[16 + 2 * j]);
-      const float b = silu(__uint_as_float(r[2 * j + 1])) * __uint_as_float(r[17 + 2 * j]);
+      const float a = gate_act(epilogue, __uint_as_float(r[2 * j])) * __uint_as_float(r[16 + 2 * j]);
+      const float b = gate_act(epilogue, __uint_as_float(r[2 * j + 1])) * __uint_as_float(r[17 + 2 * j]);
       __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
       packed[j] = *reinterpret_cast<uint32_t*>(&v);
     }
@@ -414,7 +421,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __
   pdl_wait();
   pdl_launch_dependents();
   const int64_t plane = (int64_t)tokens * features;
-  if (epilogue == EPI_SWIGLU) {
+  if (is_gated(epilogue)) {
     const int64_t n = (int64_t)tokens * (features / 2);
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
       const int64_t t = i / (features / 2);
@@ -425,7 +432,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __
         g += partial[s * plane + t * features + row_g];
         u += partial[s * plane + t * features + row_u];
       }
-      reinterpret_cast<bf16*>(out)[t * ld_out + f] = __float2bfloat16_rn(silu(g) * u);
+      reinterpret_cast<bf16*>(out)[t * ld_out + f] = __float2bfloat16_rn(gate_act(epilogue, g) * u);
     }
     return;
   }
@@ -534,11 +541,11 @@ VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, i
                             float* workspace, int64_t workspace_elems, int defer_reduce, int w_packed, unsigned* status,
                             cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && vosti_gemm_tc_supported(features, k), "gemm_tc: unsupported sizes F=%d K=%d", features, k);
-  VOSTI_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "gemm_tc: unknown epilogue %d", epilogue);
-  VOSTI_REQUIRE(epilogue != EPI_SWIGLU || features % 32 == 0, "gemm_tc: fused SiLU*up needs features %% 32 == 0");
+  VOSTI_REQUIRE((epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU) || is_gated(epilogue), "gemm_tc: unknown epilogue %d", epilogue);
+  VOSTI_REQUIRE(!is_gated(epilogue) || features % 32 == 0, "gemm_tc: a fused act(gate)*up needs features %% 32 == 0");
   VOSTI_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
   if (tokens == 0) return VOSTI_OK;
-  const int ld_out = epilogue == EPI_SWIGLU ? features / 2 : features;
+  const int ld_out = is_gated(epilogue) ? features / 2 : features;
   const int k_blocks = (k + BK - 1) / BK;
   const int splits = vosti_gemm_tc_splits(tokens, features, k);
   VOSTI_REQUIRE(splits == 1 || (workspace != nullptr && workspace_elems >= (int64_t)splits * tokens * features),

@@ -167,7 +167,8 @@ template <typename TO>
 __global__ void __launch_bounds__(256)
 post_norm_stream_kernel(const float* stream, float alpha, const void* __restrict__ t1, int t1_f32, const void* __restrict__ t2,
                         int t2_f32, const void* __restrict__ weight, int w_f32, float offset, float eps, float* stream_out,
-                        TO* __restrict__ out, int width) {
+                        TO* __restrict__ out, int width, int t1_splits, int64_t t1_plane) {
+  // t1_splits > 1: t1 is float32 [splits, rows, width], the unsummed K splits of a product, added in split order
   __shared__ float scratch[32];
   pdl_wait();
   pdl_launch_dependents();
@@ -176,11 +177,24 @@ post_norm_stream_kernel(const float* stream, float alpha, const void* __restrict
   auto sum4 = [&](int i) {
     float4 x = *reinterpret_cast<const float4*>(stream + base + i);
     x = make_float4(x.x * alpha, x.y * alpha, x.z * alpha, x.w * alpha);
+    if (t1_splits > 1) {
+      const float* p = reinterpret_cast<const float*>(t1) + base + i;
+      float4 a = *reinterpret_cast<const float4*>(p);
+      for (int s = 1; s < t1_splits; ++s) {
+        const float4 b = *reinterpret_cast<const float4*>(p + s * t1_plane);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+      }
+      x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w;
+    } else
     if (t1 != nullptr) { const float4 a = load_flex4(t1, t1_f32, base + i); x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
     if (t2 != nullptr) { const float4 a = load_flex4(t2, t2_f32, base + i); x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
     return x;
   };
-  auto sum1 = [&](int i) { return (stream[base + i] * alpha + term_at(t1, t1_f32, base + i)) + term_at(t2, t2_f32, base + i); };
+  auto sum1 = [&](int i) {
+    float a = term_at(t1, t1_f32, base + i);
+    for (int s = 1; s < t1_splits; ++s) a += reinterpret_cast<const float*>(t1)[s * t1_plane + base + i];
+    return (stream[base + i] * alpha + a) + term_at(t2, t2_f32, base + i);
+  };
   float ss = 0.f;
   if (vec) {
     for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
@@ -376,19 +390,21 @@ VOSTI_API int vosti_branch_sum(const void* const* xs, const int* x_f32, const fl
 }
 
 // Norm after the sum (see post_norm_stream_kernel): stream float32 [rows, width]; t1, t2 (either may be
-// null) float32 or bfloat16; stream_out float32 (may be `stream`) and / or out in the output type.
+// null) float32 or bfloat16, or t1 the float32 [t1_splits, rows, width] unsummed K splits of a product; stream_out float32 (may be `stream`) and / or out in the output type.
 VOSTI_API int vosti_post_norm_stream(const float* stream, float alpha, const void* t1, int t1_f32, const void* t2, int t2_f32,
                                      const void* weight, int w_f32, float offset, float eps, float* stream_out, void* out,
-                                     int out_f32, int rows, int width, cudaStream_t stream_id) {
+                                     int out_f32, int rows, int width, int t1_splits, cudaStream_t stream_id) {
+  VOSTI_REQUIRE(t1_splits >= 1 && (t1_splits == 1 || (t1 != nullptr && t1_f32)), "post_norm_stream: unsummed splits are float32");
+  const int64_t plane = (int64_t)rows * width;
   VOSTI_REQUIRE(rows >= 0 && width > 0, "post_norm_stream: bad sizes rows=%d width=%d", rows, width);
   VOSTI_REQUIRE(stream != nullptr && weight != nullptr, "post_norm_stream: a stream and a weight are needed");
   VOSTI_REQUIRE(out != nullptr || stream_out != nullptr, "post_norm_stream: nowhere to write");
   if (rows == 0) return VOSTI_OK;
   if (out_f32)
     vosti_launch(post_norm_stream_kernel<float>, dim3(rows), dim3(256), 0, stream_id, stream, alpha, t1, t1_f32, t2, t2_f32, weight,
-                 w_f32, offset, eps, stream_out, (float*)out, width);
+                 w_f32, offset, eps, stream_out, (float*)out, width, t1_splits, plane);
   else
     vosti_launch(post_norm_stream_kernel<bf16>, dim3(rows), dim3(256), 0, stream_id, stream, alpha, t1, t1_f32, t2, t2_f32, weight,
-                 w_f32, offset, eps, stream_out, (bf16*)out, width);
+                 w_f32, offset, eps, stream_out, (bf16*)out, width, t1_splits, plane);
   VOSTI_LAUNCH_CHECK();
 }

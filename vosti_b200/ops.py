@@ -171,7 +171,7 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 GLU_ACTIVATIONS = {"silu": 0, "relu": 1, "relu2": 2}
-FUSED_GLU_ACTIVATIONS = ("silu",)         # those the tensor-core product's gated epilogue takes
+FUSED_GLU_ACTIVATIONS = {"silu": 2, "relu": 4, "relu2": 5}         # the tensor-core product's gated epilogues
 
 
 def glu_mul(gate_up: torch.Tensor, activation: str) -> torch.Tensor:
@@ -409,7 +409,8 @@ def gemm_tc(x: torch.Tensor, w, status: torch.Tensor, *, out_dtype: Optional[tor
             swiglu: bool = False, allow_partial: bool = False, activation: str = "silu"):
     """y = x @ w.T on the tensor cores (bfloat16 operands, float32 accumulation); w is a
     [features, k] tensor or a `PackedWeight`. With `swiglu` the rows of w are blocks of 16 gate
-    rows followed by their 16 up rows and y = silu(gate) * up has half as many columns."""
+    rows followed by their 16 up rows and y = act(gate) * up has half as many columns, act being
+    `activation`: "silu", "relu" or "relu2" (the square of relu)."""
     packed = isinstance(w, PackedWeight)
     w_data = w.data if packed else w
     _contig(x, w_data)
@@ -422,8 +423,8 @@ def gemm_tc(x: torch.Tensor, w, status: torch.Tensor, *, out_dtype: Optional[tor
     out_dtype = out_dtype or torch.bfloat16
     if swiglu:
         if activation not in FUSED_GLU_ACTIVATIONS:
-            raise KernelError(f"gemm_tc: the gated epilogue takes {FUSED_GLU_ACTIVATIONS}, not '{activation}'")
-        epilogue, width = EPI_SWIGLU, features // 2
+            raise KernelError(f"gemm_tc: the gated epilogue takes {sorted(FUSED_GLU_ACTIVATIONS)}, not '{activation}'")
+        epilogue, width = FUSED_GLU_ACTIVATIONS[activation], features // 2
         if out_dtype != torch.bfloat16:
             raise KernelError("gemm_tc: the fused SiLU*up epilogue writes bfloat16")
     else:
@@ -433,7 +434,7 @@ def gemm_tc(x: torch.Tensor, w, status: torch.Tensor, *, out_dtype: Optional[tor
     splits = lib.vosti_gemm_tc_splits(tokens, features, k)
     elems = splits * tokens * features if splits > 1 else 0
     ws = _workspace(x.device, elems, "split_k") if elems else None
-    defer = bool(allow_partial and splits > 1 and epilogue == EPI_BF16)
+    defer = bool(allow_partial and splits > 1 and epilogue in (EPI_BF16, EPI_F32))
     out = None if defer else torch.empty((tokens, width), dtype=out_dtype, device=x.device)
     if splits > 1:
         _SPLIT_GENERATION += 1
@@ -807,7 +808,12 @@ def post_norm_stream(stream: torch.Tensor, x, weight: torch.Tensor, alpha: float
                      offset: float = 0.0, in_place: bool = True) -> "StreamPair":
     """Norm after the sum: s = alpha * stream + x in float32 (x: a tensor or a `DeferredSum`),
     y = s / sqrt(mean(s^2) + eps) * (offset + weight). y becomes the stream (float32, written over the
-    old one with `in_place`) and, rounded to `out_dtype`, the next sublayer's input."""
+    old one with `in_place`) and, rounded to `out_dtype`, the next sublayer's input. x may be a float32
+    product's unsummed K splits (`PartialSum`), which the kernel adds in split order."""
+    splits = 1
+    if isinstance(x, PartialSum) and x.dtype == torch.float32:
+        x.check()
+        splits, x = x.splits, x.partial[: x.splits * x.rows * x.width].view(x.splits * x.rows, x.width)[: x.rows]
     terms, flat = _terms(x)
     _contig(stream, weight)
     if stream.dtype != torch.float32:
@@ -819,7 +825,7 @@ def post_norm_stream(stream: torch.Tensor, x, weight: torch.Tensor, alpha: float
     out = None if out_dtype == torch.float32 else torch.empty((rows, width), dtype=out_dtype, device=stream.device)
     _check(library().vosti_post_norm_stream(_p(stream), ctypes.c_float(alpha), *flat, _p(weight), _is_f32(weight),
                                             ctypes.c_float(offset), ctypes.c_float(eps), _p(new), _p(out), 0, rows, width,
-                                            _stream()), "post_norm_stream")
+                                            splits, _stream()), "post_norm_stream")
     return StreamPair(new if out is None else out, new)
 
 
@@ -948,14 +954,24 @@ def qkv_heads(proj: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Opti
     `magnitude`); all in float32, rounded once to `out_dtype`. The queries are returned
     [tokens, nq * maps * dk]; keys and values go to their cache slots ([pages, nkv, page_size,
     maps * dk] and [pages, nkv, page_size, dv]). `maps` > 1: the projection holds `maps` query heads
-    a head and `maps` key heads a kv head, head by head. `expanded_width` D > 0 lays every map out as
+    a head and `maps` key heads a kv head, head by head. `proj` may be a float32 product's unsummed
+    K splits (`PartialSum`): the kernel adds them in split order, and the call returns (queries, the
+    summed float32 columns that follow q | k | v, or None if there are none). `expanded_width` D > 0 lays every map out as
     a head of its own, D wide, for kernels that know one map a head and one width: queries
     [tokens, nq * maps * D] and caches [pages, nkv * maps, page_size, D] with zeros after a head's own
     elements, a kv head's values stored once for each of its maps."""
+    splits, extra = 1, None
+    width = (nq + nkv) * maps * dk + nkv * dv
+    if isinstance(proj, PartialSum) and proj.dtype == torch.float32:
+        # the product's unsummed K splits: added here; columns after q | k | v (a gate) come back summed
+        proj.check()
+        splits, rows, full = proj.splits, proj.rows, proj.width
+        proj = proj.partial[: splits * rows * full].view(splits * rows, full)[:rows]
+        if full > width:
+            extra = torch.empty((rows, full - width), dtype=torch.float32, device=proj.device)
     proj = materialize(proj)
     _contig(k_cache, v_cache, positions, slot_mapping, freq, bias, q_norm, k_norm)
     tokens = proj.shape[0]
-    width = (nq + nkv) * maps * dk + nkv * dv
     if proj.dim() != 2 or proj.stride(1) != 1 or proj.shape[1] < width:
         raise KernelError("qkv_heads: the projection is [tokens, >= q | k | v columns] with contiguous rows")
     if bias is not None and (bias.dtype != torch.float32 or bias.shape[0] != width):
@@ -979,8 +995,9 @@ def qkv_heads(proj: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Opti
                                      _p(v_cache), _p(positions), _p(slot_mapping), ctypes.c_int64(num_slots), page_size, tokens,
                                      nq, nkv, maps, dk, dv, _p(q_norm), _p(k_norm), norm_flag, ctypes.c_float(eps), _p(freq),
                                      0 if freq is None else freq.shape[0], int(bool(interleaved)), ctypes.c_float(magnitude),
-                                     int(D > 0), D, D, 1 if out_dtype == torch.float32 else 0, _p(status), _stream()), "qkv_heads")
-    return q
+                                     int(D > 0), D, D, splits, _p(extra), 0 if extra is None else extra.shape[1],
+                                     1 if out_dtype == torch.float32 else 0, _p(status), _stream()), "qkv_heads")
+    return q if splits == 1 else (q, extra)
 
 
 def _attention_sink_rows(ctx, q, k_cache, v_cache, out, group, *, token_list, count, nq, nkv, dk, dv, scale, window,

@@ -63,6 +63,7 @@ class SwiGLU(FeedForward):
         self.names = tuple(spec.get("tensor_names") or ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
         self.float32_out = bool(spec.get("float32_out", False))
         self.activation = str(spec.get("activation", "silu") or "silu")
+        self.partial_out = bool(spec.get("partial_out", False))   # with float32_out: the next kernel sums the down product's K splits
         if self.activation not in ops.GLU_ACTIVATIONS:
             raise ConfigError(f"swiglu: activation is one of {sorted(ops.GLU_ACTIVATIONS)}")
         self.w_gate_up = self.w_down = None
@@ -84,7 +85,7 @@ class SwiGLU(FeedForward):
     def forward(self, ctx, x):
         mlp = gated_activation(ctx, x, self.w_gate_up, self.fused, self.activation)
         if self.float32_out:
-            return linear(ctx, mlp, self.w_down, out_dtype=torch.float32)
+            return linear(ctx, mlp, self.w_down, out_dtype=torch.float32, allow_partial=self.partial_out)
         return linear(ctx, mlp, self.w_down, allow_partial=True)     # summed by the norm that follows
 
 
@@ -140,6 +141,7 @@ class ExpertMixture(FeedForward):
         self.has_correction = bool(spec.get("correction", False))
         self.groups, self.keep = int(spec.get("groups", 1) or 1), int(spec.get("keep", 1) or 1)
         self.shared = int(spec.get("shared", 0) or 0)
+        self.partial_out = bool(spec.get("partial_out", False))
         self.activation = spec.get("activation") or ("gelu" if not self.gated else None)
         self.correction = None
         if self.experts <= 0 or not 0 < self.top <= self.experts + self.identity or self.inter <= 0:
@@ -214,10 +216,10 @@ class ExpertMixture(FeedForward):
             gate_row=bool(self.shared), scale=self.scale)
         act = ops.moe_scale(ops.materialize(linear(ctx, x, self.w_gate_up)), dense, self.inter, activation=self.activation,
                             tail=self.shared)
-        y = linear(ctx, act, self.w_down, out_dtype=torch.float32)
+        y = linear(ctx, act, self.w_down, out_dtype=torch.float32, allow_partial=self.partial_out and not self.identity)
         if self.identity:
             y = ops.moe_identity(y, ident, x)
-        return y if self.float32_out else ops.stream_sum(None, y, out_dtype=x.dtype)
+        return y if self.float32_out else ops.stream_sum(None, ops.materialize(y), out_dtype=x.dtype)
 
     def first_weight(self):
         return self.w_gate_up

@@ -33,6 +33,8 @@ of them optional and a parameter of the spec:
   exp(lq1 . lk1) - exp(lq2 . lk2) + `diff` (vectors of the head's width), then divided by its root
   mean square over the head's values (`out_norm_eps` inside the root, no weight) and multiplied by
   1 - `diff`;
+* `partial_out`: the output projection may come back as unsummed K splits (`ops.PartialSum`) for an
+  arrangement whose next kernel adds them (the norm after the sum);
 * `out_gate`: the concatenated heads are multiplied element by element by sigmoid(W_g x) (`g`), a
   product of the mixer's own input, before the output projection.
 
@@ -103,6 +105,7 @@ class SinkAttention(Mixer):
         self.out_gate = bool(spec.get("out_gate", False))
         self.lam = 0.0
         self.expanded = 0
+        self.partial_out = bool(spec.get("partial_out", False))     # the block's next kernel sums the output product's K splits
         self.b_qkv = self.q_norm = self.k_norm = None
         if self.maps not in (1, 2):
             raise ConfigError("sink_attention: a head has one score map or two")
@@ -210,32 +213,34 @@ class SinkAttention(Mixer):
                               widths=(self.maps * self.dk, self.dv))
 
     def _forward_by_heads(self, ctx, x, cache, writes_cache, group):
-        proj = linear(ctx, x, self.w_qkv, out_dtype=torch.float32)
+        proj = linear(ctx, x, self.w_qkv, out_dtype=torch.float32, allow_partial=True)   # K splits are summed by qkv_heads
         rotation = self.rotation
+        width = (self.nq + self.nkv) * self.maps * self.dk + self.nkv * self.dv
         q = ops.qkv_heads(proj, cache.k if writes_cache else None, cache.v if writes_cache else None, nq=self.nq, nkv=self.nkv,
                           maps=self.maps, dk=self.dk, dv=self.dv, page_size=group.page_size, positions=ctx.positions,
                           slot_mapping=group.slot_mapping, out_dtype=ctx.dtype, status=ctx.status, bias=self.b_qkv,
                           q_norm=self.q_norm, k_norm=self.k_norm, eps=self.head_norm_eps or 0.0, freq=self.freq,
                           interleaved=bool(rotation is not None and rotation.interleaved), magnitude=self.magnitude,
                           expanded_width=self.expanded)
+        if isinstance(proj, ops.PartialSum):
+            q, gate = q
+        else:
+            gate = proj[:, width:] if self.out_gate else None
         if self.expanded:
             D, m = self.expanded, self.maps
             each = ops.attention_sink(ctx, q, cache.k, cache.v, group, nq=self.nq * m, nkv=self.nkv * m, dk=D, dv=D,
                                       scale=self.scale, window=self.window, bias=None, sink=None, chunk=self.chunk)
-            width = (self.nq + self.nkv) * m * self.dk + self.nkv * self.dv
-            finish = ops.HeadFinish(lam=self.lam, unit_norm=True, eps=self.out_norm_eps, out_scale=1.0 - self.diff,
-                                    gate=proj[:, width:] if self.out_gate else None)
+            finish = ops.HeadFinish(lam=self.lam, unit_norm=True, eps=self.out_norm_eps, out_scale=1.0 - self.diff, gate=gate)
             attn = ops.head_finish(each, finish, nq=self.nq, maps=m, dv=self.dv, in_width=D, pair_group=self.nq // self.nkv)
-            return linear(ctx, attn, self.w_o, out_dtype=torch.float32)
+            return linear(ctx, attn, self.w_o, out_dtype=torch.float32, allow_partial=self.partial_out)
         finish = None
         if self.maps == 2 or self.out_gate:
-            width = (self.nq + self.nkv) * self.maps * self.dk + self.nkv * self.dv
             finish = ops.HeadFinish(lam=self.lam, unit_norm=self.maps == 2, eps=self.out_norm_eps, out_scale=1.0 - self.diff,
-                                    gate=proj[:, width:] if self.out_gate else None)
+                                    gate=gate)
         attn = ops.attention_sink(ctx, q, cache.k, cache.v, group, nq=self.nq, nkv=self.nkv, dk=self.dk, dv=self.dv,
                                   scale=self.scale, window=self.window, bias=self.bias_table, sink=self.sink, chunk=self.chunk,
                                   maps=self.maps, finish=finish)
-        return linear(ctx, attn, self.w_o, out_dtype=torch.float32)
+        return linear(ctx, attn, self.w_o, out_dtype=torch.float32, allow_partial=self.partial_out)
 
     def forward(self, ctx, x, cache, writes_cache: bool = True):
         group = ctx.group(cache.group)
