@@ -263,8 +263,9 @@ head_finish_kernel(const T* __restrict__ a, T* __restrict__ out, int tokens, int
 // queries go out dk_out wide (zeros after the first dk elements), the caches are
 // [pages, nkv * maps, page_size, dk_out | dv_out], key head number kv * maps + m, a kv head's values
 // written once for each of its maps, zeros after the first dk (dv) elements.
-template <typename T>
-__global__ void __launch_bounds__(256)
+// R: elements of a head a lane holds (heads of up to 32 * R elements).
+template <typename T, int R>
+__global__ void __launch_bounds__(256, R <= 4 ? 4 : 2)
 qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_stride, const float* __restrict__ bias,
                  T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ positions,
                  const int* __restrict__ slot_mapping, int64_t num_slots, int page_size, int nq, int nkv, int maps, int dk, int dv,
@@ -277,11 +278,6 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
   extern __shared__ float heads_smem[];          // [2 * rot_half] cosines and sines, then [warps][dk] a head per warp
   pdl_wait();
   pdl_launch_dependents();
-  auto value = [&](int64_t i) {
-    float x = load_flex(proj, proj_f32, i);
-    for (int sp = 1; sp < splits; ++sp) x += reinterpret_cast<const float*>(proj)[sp * plane + i];
-    return x;
-  };
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   float* turn = heads_smem;
   float* buf = heads_smem + 2 * rot_half + warp * dk;
@@ -308,12 +304,23 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
   const int nqm = nq * maps, nkm = nkv * maps;
   const int64_t wq = (int64_t)nqm * dk, wk = (int64_t)nkm * dk;
   const int64_t row = (int64_t)t * proj_stride;
-  const int pieces = extra_out != nullptr ? (extra_width + 255) / 256 : 0;       // the extra columns, 256 a warp
+  const int pieces = extra_out != nullptr ? (extra_width + 32 * R - 1) / (32 * R) : 0;       // the extra columns, 32 * R a warp
   for (int hd = blockIdx.y * nwarps + warp; hd < nqm + nkm + nkv + pieces; hd += gridDim.y * nwarps) {
     if (hd >= nqm + nkm + nkv) {
       const int64_t off = wq + wk + (int64_t)nkv * dv;
-      const int c0 = (hd - nqm - nkm - nkv) * 256;
-      for (int i = c0 + lane; i < min(c0 + 256, extra_width); i += 32) extra_out[(int64_t)t * extra_width + i] = value(row + off + i);
+      const int c0 = (hd - nqm - nkm - nkv) * 32 * R;
+      float g[R];
+#pragma unroll
+      for (int j = 0; j < R; ++j) g[j] = c0 + lane + 32 * j < extra_width ? load_flex(proj, proj_f32, row + off + c0 + lane + 32 * j) : 0.f;
+      for (int sp = 1; sp < splits; ++sp) {
+        const float* p = reinterpret_cast<const float*>(proj) + sp * plane + row + off + c0;
+#pragma unroll
+        for (int j = 0; j < R; ++j)
+          if (c0 + lane + 32 * j < extra_width) g[j] += p[lane + 32 * j];
+      }
+#pragma unroll
+      for (int j = 0; j < R; ++j)
+        if (c0 + lane + 32 * j < extra_width) extra_out[(int64_t)t * extra_width + c0 + lane + 32 * j] = g[j];
       continue;
     }
     if (hd >= nqm + nkm) {                         // a value head: bias, then its cache slot
@@ -324,7 +331,8 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
         for (int i = lane; i < dv_out; i += 32) {
           float x = 0.f;
           if (i < dv) {
-            x = value(row + off + i);
+            x = load_flex(proj, proj_f32, row + off + i);
+            for (int sp = 1; sp < splits; ++sp) x += reinterpret_cast<const float*>(proj)[sp * plane + row + off + i];
             if (bias != nullptr) x += bias[off + i];
           }
           for (int c = 0; c < maps; ++c) v_cache[((page * nkm + g * maps + c) * page_size + offset) * dv_out + i] = from_f32<T>(x);
@@ -333,7 +341,8 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
       }
       T* dst = v_cache + ((page * nkv + g) * page_size + offset) * dv;
       for (int i = lane; i < dv; i += 32) {
-        float x = value(row + off + i);
+        float x = load_flex(proj, proj_f32, row + off + i);
+        for (int sp = 1; sp < splits; ++sp) x += reinterpret_cast<const float*>(proj)[sp * plane + row + off + i];
         if (bias != nullptr) x += bias[off + i];
         dst[i] = from_f32<T>(x);
       }
@@ -343,14 +352,25 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
     if (!is_q && !store) continue;
     const int64_t off = (int64_t)hd * dk;          // query heads, then key heads, in the projection's order
     const void* norm_w = is_q ? q_norm : k_norm;
-    float x[MAX_W / 32];
+    float x[R], nw[R];
     float ss = 0.f;
+    // the loads of one split (and the norm's weights) are in flight together; splits are added in split order
 #pragma unroll
-    for (int j = 0; j < MAX_W / 32; ++j) {
+    for (int j = 0; j < R; ++j) {
       const int i = lane + 32 * j;
-      x[j] = 0.f;
+      x[j] = i < dk ? load_flex(proj, proj_f32, row + off + i) : 0.f;
+      nw[j] = (norm_w != nullptr && i < dk) ? load_flex(norm_w, norm_f32, i) : 1.f;
+    }
+    for (int sp = 1; sp < splits; ++sp) {
+      const float* p = reinterpret_cast<const float*>(proj) + sp * plane + row + off;
+#pragma unroll
+      for (int j = 0; j < R; ++j)
+        if (lane + 32 * j < dk) x[j] += p[lane + 32 * j];
+    }
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      const int i = lane + 32 * j;
       if (i < dk) {
-        x[j] = value(row + off + i);
         if (bias != nullptr) x[j] += bias[off + i];
         ss += x[j] * x[j];
       }
@@ -358,10 +378,7 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
     if (norm_w != nullptr) {
       const float inv = 1.f / sqrtf(warp_sum(ss) / (float)dk + eps);
 #pragma unroll
-      for (int j = 0; j < MAX_W / 32; ++j) {
-        const int i = lane + 32 * j;
-        if (i < dk) x[j] = x[j] * inv * load_flex(norm_w, norm_f32, i);
-      }
+      for (int j = 0; j < R; ++j) x[j] = x[j] * inv * nw[j];
     }
     T* dst;
     if (is_q) {
@@ -375,11 +392,11 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
       for (int i = dk + lane; i < dk_out; i += 32) dst[i] = from_f32<T>(0.f);
     if (rot_half > 0) {
 #pragma unroll
-      for (int j = 0; j < MAX_W / 32; ++j)
+      for (int j = 0; j < R; ++j)
         if (lane + 32 * j < dk) buf[lane + 32 * j] = x[j];
       __syncwarp();
 #pragma unroll
-      for (int j = 0; j < MAX_W / 32; ++j) {
+      for (int j = 0; j < R; ++j) {
         const int i = lane + 32 * j;
         if (i < 2 * rot_half) {
           const bool first = interleaved ? (i & 1) == 0 : i < rot_half;
@@ -392,7 +409,7 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
       __syncwarp();
     }
 #pragma unroll
-    for (int j = 0; j < MAX_W / 32; ++j) {
+    for (int j = 0; j < R; ++j) {
       const int i = lane + 32 * j;
       if (i < dk) dst[i] = from_f32<T>(x[j]);
     }
@@ -729,15 +746,20 @@ VOSTI_API int vosti_qkv_heads(const void* proj, int proj_f32, long long proj_str
   if (tokens == 0) return VOSTI_OK;
   const int threads = 256;
   const size_t smem = ((size_t)2 * rot_half + (size_t)(threads / 32) * dk) * sizeof(float);
-  const int items = (nq + nkv) * maps + nkv + (extra_out != nullptr ? (extra_width + 255) / 256 : 0);
-  const dim3 grid(tokens, (items + threads / 32 - 1) / (threads / 32));
-  if (is_f32)
-    vosti_launch(qkv_heads_kernel<float>, grid, dim3(threads), smem, stream, proj, proj_f32, (int64_t)proj_stride, bias, (float*)q_out,
-                 (float*)k_cache, (float*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, maps, dk, dv, q_norm, k_norm,
-                 norm_f32, eps, freq, rot_half, interleaved, magnitude, expanded, dk_out, dv_out, splits, plane, extra_out, extra_width, status);
-  else
-    vosti_launch(qkv_heads_kernel<bf16>, grid, dim3(threads), smem, stream, proj, proj_f32, (int64_t)proj_stride, bias, (bf16*)q_out,
-                 (bf16*)k_cache, (bf16*)v_cache, positions, slot_mapping, num_slots, page_size, nq, nkv, maps, dk, dv, q_norm, k_norm,
-                 norm_f32, eps, freq, rot_half, interleaved, magnitude, expanded, dk_out, dv_out, splits, plane, extra_out, extra_width, status);
+  const int r = (dk <= 128 && dv <= 128) ? 4 : 8;
+  const int items = (nq + nkv) * maps + nkv + (extra_out != nullptr ? (extra_width + 32 * r - 1) / (32 * r) : 0);
+  // few tokens: a warp a head; many: a block a token, so that a token's angles are formed once
+  const dim3 grid(tokens, tokens < 64 ? (items + threads / 32 - 1) / (threads / 32) : 1);
+#define VOSTI_HEADS_ARGS(T) proj, proj_f32, (int64_t)proj_stride, bias, (T*)q_out, (T*)k_cache, (T*)v_cache, positions, slot_mapping,  \
+                            num_slots, page_size, nq, nkv, maps, dk, dv, q_norm, k_norm, norm_f32, eps, freq, rot_half, interleaved, \
+                            magnitude, expanded, dk_out, dv_out, splits, plane, extra_out, extra_width, status
+  if (is_f32) {
+    if (r == 4) vosti_launch(qkv_heads_kernel<float, 4>, grid, dim3(threads), smem, stream, VOSTI_HEADS_ARGS(float));
+    else vosti_launch(qkv_heads_kernel<float, 8>, grid, dim3(threads), smem, stream, VOSTI_HEADS_ARGS(float));
+  } else {
+    if (r == 4) vosti_launch(qkv_heads_kernel<bf16, 4>, grid, dim3(threads), smem, stream, VOSTI_HEADS_ARGS(bf16));
+    else vosti_launch(qkv_heads_kernel<bf16, 8>, grid, dim3(threads), smem, stream, VOSTI_HEADS_ARGS(bf16));
+  }
+#undef VOSTI_HEADS_ARGS
   VOSTI_LAUNCH_CHECK();
 }

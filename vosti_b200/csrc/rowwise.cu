@@ -12,7 +12,8 @@
 template <typename T, typename TO = T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restrict__ source,
                                  const int* __restrict__ values, const T* __restrict__ table,
-                                 TO* __restrict__ out, int hidden, int vocab, float scale, unsigned* status) {
+                                 TO* __restrict__ out, int hidden, int vocab, float scale, unsigned* status,
+                                 bf16* __restrict__ rounded = nullptr) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -26,9 +27,36 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restr
   const T* src = table + (int64_t)id * hidden;
   TO* dst = out + (int64_t)t * hidden;
   const int bytes = hidden * (int)sizeof(T);
-  if (scale != 1.f || sizeof(TO) != sizeof(T)) {
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-      dst[i] = bad ? from_f32<TO>(0.f) : from_f32<TO>(to_f32(src[i]) * scale);
+  if (sizeof(TO) == 4 && sizeof(T) == 2 && hidden % 8 == 0) {
+    // a float32 stream from a bfloat16 table: 16-byte words in, two out, and the row's rounding beside it if asked for
+    const uint4* s8 = reinterpret_cast<const uint4*>(src);
+    for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) {
+      const uint4 raw = bad ? make_uint4(0, 0, 0, 0) : s8[i];
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p[e]);
+        v[2 * e] = f.x * scale;
+        v[2 * e + 1] = f.y * scale;
+      }
+      float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + (int64_t)i * 8);
+      d[0] = make_float4(v[0], v[1], v[2], v[3]);
+      d[1] = make_float4(v[4], v[5], v[6], v[7]);
+      if (rounded != nullptr) {
+        uint4 r;
+        __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) q[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+        reinterpret_cast<uint4*>(rounded + (int64_t)t * hidden)[i] = r;
+      }
+    }
+  } else if (scale != 1.f || sizeof(TO) != sizeof(T) || rounded != nullptr) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float v = bad ? 0.f : to_f32(src[i]) * scale;
+      dst[i] = from_f32<TO>(v);
+      if (rounded != nullptr) rounded[(int64_t)t * hidden + i] = __float2bfloat16_rn(v);
+    }
   } else if (bytes % 16 == 0) {
     const int4* s4 = reinterpret_cast<const int4*>(src);
     int4* d4 = reinterpret_cast<int4*>(dst);
@@ -45,23 +73,24 @@ VOSTI_API int vosti_embedding(const int* ids, const int* source, const int* valu
                 tokens, hidden, vocab);
   if (tokens == 0) return VOSTI_OK;
   if (is_f32)
-    vosti_launch(embedding_kernel<float>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const float*)table, (float*)out, hidden, vocab, scale, status);
+    vosti_launch(embedding_kernel<float>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const float*)table, (float*)out, hidden, vocab, scale, status, (bf16*)nullptr);
   else
-    vosti_launch(embedding_kernel<bf16>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const bf16*)table, (bf16*)out, hidden, vocab, scale, status);
+    vosti_launch(embedding_kernel<bf16>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const bf16*)table, (bf16*)out, hidden, vocab, scale, status, (bf16*)nullptr);
   VOSTI_LAUNCH_CHECK();
 }
 
 // The same with float32 rows whatever the table's type: the start of a float32 residual stream
 // (a bfloat16 entry times the scale is not rounded again).
+// `rounded` (or null): the same rows rounded to bfloat16, for products that read the stream's rounding.
 VOSTI_API int vosti_embedding_stream(const int* ids, const int* source, const int* values, const void* table, float* out,
-                                     int tokens, int hidden, int vocab, int is_f32, float scale, unsigned* status,
+                                     void* rounded, int tokens, int hidden, int vocab, int is_f32, float scale, unsigned* status,
                                      cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes T=%d H=%d V=%d", tokens, hidden, vocab);
   if (tokens == 0) return VOSTI_OK;
   if (is_f32)
-    vosti_launch(embedding_kernel<float, float>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const float*)table, out, hidden, vocab, scale, status);
+    vosti_launch(embedding_kernel<float, float>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const float*)table, out, hidden, vocab, scale, status, (bf16*)rounded);
   else
-    vosti_launch(embedding_kernel<bf16, float>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const bf16*)table, out, hidden, vocab, scale, status);
+    vosti_launch(embedding_kernel<bf16, float>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const bf16*)table, out, hidden, vocab, scale, status, (bf16*)rounded);
   VOSTI_LAUNCH_CHECK();
 }
 

@@ -164,11 +164,13 @@ rms_stream_kernel(const float* stream, const void* t1, int t1_f32, const void* t
 // over the old one: a thread writes only what it read itself) and, rounded, the next sublayer's
 // input. The row is read twice, in the same order, so that any width works.
 template <typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 post_norm_stream_kernel(const float* stream, float alpha, const void* __restrict__ t1, int t1_f32, const void* __restrict__ t2,
                         int t2_f32, const void* __restrict__ weight, int w_f32, float offset, float eps, float* stream_out,
-                        TO* __restrict__ out, int width, int t1_splits, int64_t t1_plane) {
-  // t1_splits > 1: t1 is float32 [splits, rows, width], the unsummed K splits of a product, added in split order
+                        TO* __restrict__ out, int width, int t1_splits, int64_t t1_plane, int cached) {
+  // t1_splits > 1: t1 is float32 [splits, rows, width], the unsummed K splits of a product, added in split order.
+  // cached: the summed row is kept in shared memory (width floats) between the two passes; else it is formed twice.
+  extern __shared__ __align__(16) float row_smem[];
   __shared__ float scratch[32];
   pdl_wait();
   pdl_launch_dependents();
@@ -178,15 +180,34 @@ post_norm_stream_kernel(const float* stream, float alpha, const void* __restrict
     float4 x = *reinterpret_cast<const float4*>(stream + base + i);
     x = make_float4(x.x * alpha, x.y * alpha, x.z * alpha, x.w * alpha);
     if (t1_splits > 1) {
+      // four splits' loads in flight together, added in split order
       const float* p = reinterpret_cast<const float*>(t1) + base + i;
       float4 a = *reinterpret_cast<const float4*>(p);
-      for (int s = 1; s < t1_splits; ++s) {
+      int s = 1;
+      for (; s + 8 <= t1_splits; s += 8) {
+        float4 b[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) b[u] = *reinterpret_cast<const float4*>(p + (s + u) * t1_plane);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { a.x += b[u].x; a.y += b[u].y; a.z += b[u].z; a.w += b[u].w; }
+      }
+      for (; s + 4 <= t1_splits; s += 4) {
+        const float4 b0 = *reinterpret_cast<const float4*>(p + s * t1_plane), b1 = *reinterpret_cast<const float4*>(p + (s + 1) * t1_plane);
+        const float4 b2 = *reinterpret_cast<const float4*>(p + (s + 2) * t1_plane), b3 = *reinterpret_cast<const float4*>(p + (s + 3) * t1_plane);
+        a.x = (((a.x + b0.x) + b1.x) + b2.x) + b3.x;
+        a.y = (((a.y + b0.y) + b1.y) + b2.y) + b3.y;
+        a.z = (((a.z + b0.z) + b1.z) + b2.z) + b3.z;
+        a.w = (((a.w + b0.w) + b1.w) + b2.w) + b3.w;
+      }
+      for (; s < t1_splits; ++s) {
         const float4 b = *reinterpret_cast<const float4*>(p + s * t1_plane);
         a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
       }
       x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w;
-    } else
-    if (t1 != nullptr) { const float4 a = load_flex4(t1, t1_f32, base + i); x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
+    } else if (t1 != nullptr) {
+      const float4 a = load_flex4(t1, t1_f32, base + i);
+      x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w;
+    }
     if (t2 != nullptr) { const float4 a = load_flex4(t2, t2_f32, base + i); x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
     return x;
   };
@@ -199,18 +220,20 @@ post_norm_stream_kernel(const float* stream, float alpha, const void* __restrict
   if (vec) {
     for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
       const float4 x = sum4(i);
+      if (cached) *reinterpret_cast<float4*>(row_smem + i) = x;
       ss += (x.x * x.x + x.y * x.y) + (x.z * x.z + x.w * x.w);
     }
   } else {
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
       const float x = sum1(i);
+      if (cached) row_smem[i] = x;
       ss += x * x;
     }
   }
   const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
   if (vec) {
     for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
-      float4 x = sum4(i);
+      float4 x = cached ? *reinterpret_cast<const float4*>(row_smem + i) : sum4(i);     // (a thread reads what it wrote itself)
       const float4 w = load_flex4(weight, w_f32, i);
       x = make_float4(x.x * inv * (offset + w.x), x.y * inv * (offset + w.y), x.z * inv * (offset + w.z), x.w * inv * (offset + w.w));
       if (stream_out != nullptr) *reinterpret_cast<float4*>(stream_out + base + i) = x;
@@ -219,7 +242,7 @@ post_norm_stream_kernel(const float* stream, float alpha, const void* __restrict
     return;
   }
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    const float x = sum1(i) * inv * (offset + load_flex(weight, w_f32, i));
+    const float x = (cached ? row_smem[i] : sum1(i)) * inv * (offset + load_flex(weight, w_f32, i));
     if (stream_out != nullptr) stream_out[base + i] = x;
     if (out != nullptr) out[base + i] = from_f32<TO>(x);
   }
@@ -400,11 +423,16 @@ VOSTI_API int vosti_post_norm_stream(const float* stream, float alpha, const voi
   VOSTI_REQUIRE(stream != nullptr && weight != nullptr, "post_norm_stream: a stream and a weight are needed");
   VOSTI_REQUIRE(out != nullptr || stream_out != nullptr, "post_norm_stream: nowhere to write");
   if (rows == 0) return VOSTI_OK;
+  const int cached = width <= 12288;                     // 48 KB of shared memory hold the row
+  const size_t smem = cached ? (size_t)width * sizeof(float) : 0;
+  // few rows: a thread a 16-byte word, so that a row's loads are all in flight at once
+  int threads = 256;
+  if (rows <= 64 && width % 4 == 0) threads = width / 4 >= 1024 ? 1024 : (width / 4 + 31) / 32 * 32 > 256 ? (width / 4 + 31) / 32 * 32 : 256;
   if (out_f32)
-    vosti_launch(post_norm_stream_kernel<float>, dim3(rows), dim3(256), 0, stream_id, stream, alpha, t1, t1_f32, t2, t2_f32, weight,
-                 w_f32, offset, eps, stream_out, (float*)out, width, t1_splits, plane);
+    vosti_launch(post_norm_stream_kernel<float>, dim3(rows), dim3(threads), smem, stream_id, stream, alpha, t1, t1_f32, t2, t2_f32, weight,
+                 w_f32, offset, eps, stream_out, (float*)out, width, t1_splits, plane, cached);
   else
-    vosti_launch(post_norm_stream_kernel<bf16>, dim3(rows), dim3(256), 0, stream_id, stream, alpha, t1, t1_f32, t2, t2_f32, weight,
-                 w_f32, offset, eps, stream_out, (bf16*)out, width, t1_splits, plane);
+    vosti_launch(post_norm_stream_kernel<bf16>, dim3(rows), dim3(threads), smem, stream_id, stream, alpha, t1, t1_f32, t2, t2_f32, weight,
+                 w_f32, offset, eps, stream_out, (bf16*)out, width, t1_splits, plane, cached);
   VOSTI_LAUNCH_CHECK();
 }

@@ -88,11 +88,13 @@ def _contig(*tensors):
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor,
-              feedback: Optional[tuple] = None, scale: float = 1.0, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+              feedback: Optional[tuple] = None, scale: float = 1.0, out_dtype: Optional[torch.dtype] = None,
+              rounded: bool = False):
     """table[ids] * scale. `feedback` = (source, values), int32: row t takes values[source[t]] as
     its id where source[t] >= 0 (a token sampled on the device that the host has not read yet).
     `out_dtype` float32 gives float32 rows from a bfloat16 table (the scaled entry is not rounded
-    again): the start of a float32 residual stream."""
+    again): the start of a float32 residual stream; with `rounded` the call returns a `StreamPair` of
+    those rows and their rounding to bfloat16, written by the same kernel."""
     _contig(ids, table)
     source, values = feedback if feedback is not None else (None, None)
     if source is not None:
@@ -100,10 +102,11 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor,
         assert source.shape[0] == ids.shape[0] and source.dtype == values.dtype == torch.int32
     if out_dtype == torch.float32 and table.dtype != torch.float32:
         out = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
-        _check(library().vosti_embedding_stream(_p(ids), _p(source), _p(values), _p(table), _p(out), ids.shape[0], table.shape[1],
-                                                table.shape[0], _is_f32(table), ctypes.c_float(scale), _p(status), _stream()),
-               "embedding")
-        return out
+        low = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.bfloat16, device=table.device) if rounded else None
+        _check(library().vosti_embedding_stream(_p(ids), _p(source), _p(values), _p(table), _p(out), _p(low), ids.shape[0],
+                                                table.shape[1], table.shape[0], _is_f32(table), ctypes.c_float(scale), _p(status),
+                                                _stream()), "embedding")
+        return StreamPair(low, out) if rounded else out
     if out_dtype is not None and out_dtype != table.dtype:
         raise KernelError("embedding: rows come in the table's type or in float32")
     out = torch.empty((ids.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)

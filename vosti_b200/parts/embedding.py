@@ -1,7 +1,9 @@
 """The embedding table: hidden rows by token id (kernels/triton_kernels/embedding.py:62-84),
 optionally multiplied by a constant `scale` in float32 (Qwen3 has none; architectures that
 scale their embeddings by sqrt(hidden) name it in their spec). `out_dtype` "float32" gives float32
-rows whatever the table's type: the start of a float32 residual stream.
+rows whatever the table's type: the start of a float32 residual stream (in bfloat16 serving the
+same kernel writes the rows' rounding beside them and the part returns both, an `ops.StreamPair`,
+for arrangements whose sublayers read the rounded stream).
 """
 from __future__ import annotations
 
@@ -34,7 +36,9 @@ class TableEmbedding(Embedding):
         return self.weight
 
     def forward(self, ctx, tokens, feedback=None):
-        return ops.embedding(tokens, self.weight, ctx.status, feedback=feedback, scale=self.scale, out_dtype=self.out_dtype)
+        pair = self.out_dtype == torch.float32 and ctx.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
+        return ops.embedding(tokens, self.weight, ctx.status, feedback=feedback, scale=self.scale, out_dtype=self.out_dtype,
+                             rounded=pair)
 
 
 register_part("embedding", "table", TableEmbedding, replace=True)
