@@ -182,6 +182,15 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
   }
 }
 
+__device__ __forceinline__ void store_four(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store_four(bf16* p, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const unsigned*>(&lo);
+  raw.y = *reinterpret_cast<const unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // What may follow a head's attention before the output projection, in float32:
 //   * with two score maps a head (differential attention): o = a1 - lambda * a2, a1 and a2 the two
 //     maps' softmax-weighted sums of the same values;
@@ -303,6 +312,11 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
   }
   const int nqm = nq * maps, nkm = nkv * maps;
   const int64_t wq = (int64_t)nqm * dk, wk = (int64_t)nkm * dk;
+  // 16-byte words when everything is float32 and lies on 16-byte borders
+  const bool vec4 = proj_f32 && (norm_f32 || (q_norm == nullptr && k_norm == nullptr)) && proj_stride % 4 == 0 && dk % 4 == 0 && dv % 4 == 0 &&
+                    (rot_half == 0 || (interleaved ? rot_half % 2 == 0 : rot_half % 4 == 0)) && (!expanded || (dk_out % 4 == 0 && dv_out % 4 == 0)) &&
+                    (reinterpret_cast<uintptr_t>(proj) & 15) == 0 && (bias == nullptr || (reinterpret_cast<uintptr_t>(bias) & 15) == 0) &&
+                    (q_norm == nullptr || (reinterpret_cast<uintptr_t>(q_norm) & 15) == 0) && (k_norm == nullptr || (reinterpret_cast<uintptr_t>(k_norm) & 15) == 0);
   const int64_t row = (int64_t)t * proj_stride;
   const int pieces = extra_out != nullptr ? (extra_width + 32 * R - 1) / (32 * R) : 0;       // the extra columns, 32 * R a warp
   for (int hd = blockIdx.y * nwarps + warp; hd < nqm + nkm + nkv + pieces; hd += gridDim.y * nwarps) {
@@ -327,6 +341,30 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
       if (!store) continue;
       const int g = hd - nqm - nkm;
       const int64_t off = wq + wk + (int64_t)g * dv;
+      if (vec4) {
+        const float* pf = reinterpret_cast<const float*>(proj) + row + off;
+        const int wide = expanded ? dv_out : dv;
+        for (int i0 = 4 * lane; i0 < wide; i0 += 128) {
+          float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (i0 < dv) {
+            x = *reinterpret_cast<const float4*>(pf + i0);
+            for (int sp = 1; sp < splits; ++sp) {
+              const float4 y = *reinterpret_cast<const float4*>(pf + sp * plane + i0);
+              x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+            }
+            if (bias != nullptr) {
+              const float4 y = *reinterpret_cast<const float4*>(bias + off + i0);
+              x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+            }
+          }
+          if (expanded) {
+            for (int c = 0; c < maps; ++c) store_four(v_cache + ((page * nkm + g * maps + c) * page_size + offset) * dv_out + i0, x);
+          } else {
+            store_four(v_cache + ((page * nkv + g) * page_size + offset) * dv + i0, x);
+          }
+        }
+        continue;
+      }
       if (expanded) {
         for (int i = lane; i < dv_out; i += 32) {
           float x = 0.f;
@@ -352,6 +390,92 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
     if (!is_q && !store) continue;
     const int64_t off = (int64_t)hd * dk;          // query heads, then key heads, in the projection's order
     const void* norm_w = is_q ? q_norm : k_norm;
+    T* dst;
+    if (is_q) {
+      dst = expanded ? q_out + ((int64_t)t * nqm + hd) * dk_out : q_out + (int64_t)t * wq + off;
+    } else {
+      const int kh = hd - nqm, g = kh / maps, m = kh % maps;
+      dst = expanded ? k_cache + ((page * nkm + kh) * page_size + offset) * dk_out
+                     : k_cache + (((page * nkv + g) * page_size + offset) * maps + m) * dk;
+    }
+    if (expanded)
+      for (int i = dk + lane; i < dk_out; i += 32) dst[i] = from_f32<T>(0.f);
+    if (vec4) {
+      // a lane takes four neighbouring elements (of every 128): 16-byte loads, one store of four
+      constexpr int C = R / 4;
+      const float* pf = reinterpret_cast<const float*>(proj) + row + off;
+      float4 xv[C], nv[C];
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        const int i0 = 4 * lane + 128 * c;
+        xv[c] = i0 < dk ? *reinterpret_cast<const float4*>(pf + i0) : make_float4(0.f, 0.f, 0.f, 0.f);
+        nv[c] = (norm_w != nullptr && i0 < dk) ? *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(norm_w) + i0)
+                                               : make_float4(1.f, 1.f, 1.f, 1.f);
+      }
+      for (int sp = 1; sp < splits; ++sp) {
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          const int i0 = 4 * lane + 128 * c;
+          if (i0 < dk) {
+            const float4 y = *reinterpret_cast<const float4*>(pf + sp * plane + i0);
+            xv[c].x += y.x; xv[c].y += y.y; xv[c].z += y.z; xv[c].w += y.w;
+          }
+        }
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        const int i0 = 4 * lane + 128 * c;
+        if (bias != nullptr && i0 < dk) {
+          const float4 y = *reinterpret_cast<const float4*>(bias + off + i0);
+          xv[c].x += y.x; xv[c].y += y.y; xv[c].z += y.z; xv[c].w += y.w;
+        }
+        ss += (xv[c].x * xv[c].x + xv[c].y * xv[c].y) + (xv[c].z * xv[c].z + xv[c].w * xv[c].w);
+      }
+      if (norm_w != nullptr) {
+        const float inv = 1.f / sqrtf(warp_sum(ss) / (float)dk + eps);
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+          xv[c] = make_float4(xv[c].x * inv * nv[c].x, xv[c].y * inv * nv[c].y, xv[c].z * inv * nv[c].z, xv[c].w * inv * nv[c].w);
+      }
+      if (rot_half > 0 && interleaved) {
+        // both elements of a pair lie in the lane's four
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          const int i0 = 4 * lane + 128 * c;
+          if (i0 < 2 * rot_half) {
+            const float c0 = turn[i0 >> 1], c1 = turn[(i0 >> 1) + 1], s0 = turn[rot_half + (i0 >> 1)], s1 = turn[rot_half + (i0 >> 1) + 1];
+            const float4 v = xv[c];
+            xv[c] = make_float4(v.x * c0 - v.y * s0, v.y * c0 + v.x * s0, v.z * c1 - v.w * s1, v.w * c1 + v.z * s1);
+          }
+        }
+      } else if (rot_half > 0) {
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+          if (4 * lane + 128 * c < dk) *reinterpret_cast<float4*>(buf + 4 * lane + 128 * c) = xv[c];
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          const int i0 = 4 * lane + 128 * c;
+          if (i0 < 2 * rot_half) {
+            const bool first = i0 < rot_half;
+            const int pair = first ? i0 : i0 - rot_half;
+            const float4 o = *reinterpret_cast<const float4*>(buf + (first ? i0 + rot_half : i0 - rot_half));
+            const float4 cs = *reinterpret_cast<const float4*>(turn + pair), sn = *reinterpret_cast<const float4*>(turn + rot_half + pair);
+            const float4 v = xv[c];
+            xv[c] = first ? make_float4(v.x * cs.x - o.x * sn.x, v.y * cs.y - o.y * sn.y, v.z * cs.z - o.z * sn.z, v.w * cs.w - o.w * sn.w)
+                          : make_float4(v.x * cs.x + o.x * sn.x, v.y * cs.y + o.y * sn.y, v.z * cs.z + o.z * sn.z, v.w * cs.w + o.w * sn.w);
+          }
+        }
+        __syncwarp();
+      }
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        const int i0 = 4 * lane + 128 * c;
+        if (i0 < dk) store_four(dst + i0, xv[c]);
+      }
+      continue;
+    }
     float x[R], nw[R];
     float ss = 0.f;
     // the loads of one split (and the norm's weights) are in flight together; splits are added in split order
@@ -380,16 +504,6 @@ qkv_heads_kernel(const void* __restrict__ proj, int proj_f32, int64_t proj_strid
 #pragma unroll
       for (int j = 0; j < R; ++j) x[j] = x[j] * inv * nw[j];
     }
-    T* dst;
-    if (is_q) {
-      dst = expanded ? q_out + ((int64_t)t * nqm + hd) * dk_out : q_out + (int64_t)t * wq + off;
-    } else {
-      const int kh = hd - nqm, g = kh / maps, m = kh % maps;
-      dst = expanded ? k_cache + ((page * nkm + kh) * page_size + offset) * dk_out
-                     : k_cache + (((page * nkv + g) * page_size + offset) * maps + m) * dk;
-    }
-    if (expanded)
-      for (int i = dk + lane; i < dk_out; i += 32) dst[i] = from_f32<T>(0.f);
     if (rot_half > 0) {
 #pragma unroll
       for (int j = 0; j < R; ++j)
