@@ -182,6 +182,13 @@ qkv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict
   }
 }
 
+__device__ __forceinline__ float4 load_four(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load_four(const bf16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
 __device__ __forceinline__ void store_four(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
 __device__ __forceinline__ void store_four(bf16* p, float4 v) {
   const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
@@ -246,6 +253,43 @@ head_finish_kernel(const T* __restrict__ a, T* __restrict__ out, int tokens, int
   const int64_t wid = (int64_t)blockIdx.x * WARPS + warp;
   if (wid >= (int64_t)tokens * nq) return;
   const int t = (int)(wid / nq), h = (int)(wid % nq);
+  if (dv % 4 == 0 && a_width % 4 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+      (f.gate == nullptr || (f.gate_f32 && f.gate_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(f.gate) & 15) == 0))) {
+    // a lane takes four neighbouring elements (of every 128): whole words in and out
+    constexpr int C = MAX_W / 128;
+    float4 o[C];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      const int i0 = 4 * lane + 128 * c;
+      o[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i0 < dv) {
+#pragma unroll
+        for (int m = 0; m < MAPS; ++m) {
+          const int64_t row = (int64_t)t * nq * MAPS + (pair_group > 0 ? h + (h / pair_group) * pair_group + m * pair_group : h * MAPS + m);
+          const float4 v = load_four(a + row * a_width + i0);
+          const float by = m == 0 ? 1.f : -f.lambda;
+          o[c].x += by * v.x; o[c].y += by * v.y; o[c].z += by * v.z; o[c].w += by * v.w;
+        }
+        ss += (o[c].x * o[c].x + o[c].y * o[c].y) + (o[c].z * o[c].z + o[c].w * o[c].w);
+      }
+    }
+    float by = 1.f;
+    if (f.unit_norm) by = f.out_scale / sqrtf(warp_sum(ss) / (float)dv + f.eps);
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      const int i0 = 4 * lane + 128 * c;
+      if (i0 < dv) {
+        float4 y = f.unit_norm ? make_float4(o[c].x * by, o[c].y * by, o[c].z * by, o[c].w * by) : o[c];
+        if (f.gate != nullptr) {
+          const float4 g = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(f.gate) + (int64_t)t * f.gate_stride + (int64_t)h * dv + i0);
+          y.x *= 1.f / (1.f + expf(-g.x)); y.y *= 1.f / (1.f + expf(-g.y)); y.z *= 1.f / (1.f + expf(-g.z)); y.w *= 1.f / (1.f + expf(-g.w));
+        }
+        store_four(out + wid * dv + i0, y);
+      }
+    }
+    return;
+  }
   float acc[MAPS][MAX_W / 32], inv[MAPS];
 #pragma unroll
   for (int m = 0; m < MAPS; ++m) {

@@ -261,6 +261,12 @@ moe_router_scored_kernel(const void* __restrict__ x, int x_f32, const float* __r
 // `gelu`: 0 no activation, 1 the exact GELU, 2 the square of relu. `tail` > 0: after the experts' slices
 // the row holds one more slice of `tail` columns (a shared expert of another width), whose weight is
 // column `experts` of dense, which then has experts + 1 columns.
+__device__ __forceinline__ float moe_activation(float x, int mode) {
+  if (mode == 1) return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+  if (mode == 2) { x = fmaxf(x, 0.f); return x * x; }
+  return x;
+}
+
 template <typename T>
 __global__ void moe_scale_kernel(T* __restrict__ act, const float* __restrict__ dense, int64_t tokens, int experts, int ff,
                                  int gelu, int tail) {
@@ -268,13 +274,32 @@ __global__ void moe_scale_kernel(T* __restrict__ act, const float* __restrict__ 
   pdl_launch_dependents();
   const int64_t width = (int64_t)experts * ff + tail, n = tokens * width;
   const int cols = experts + (tail > 0 ? 1 : 0);
+  if (sizeof(T) == 2 && ff % 8 == 0 && tail % 8 == 0 && (reinterpret_cast<uintptr_t>(act) & 15) == 0) {
+    // 16-byte words: eight elements of one expert's slice
+    const int64_t words = n / 8, per_row = width / 8;
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < words; w += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t t = w / per_row;
+      const int64_t c = (w - t * per_row) * 8;
+      const int e = c < (int64_t)experts * ff ? (int)(c / ff) : experts;
+      const float by = dense != nullptr ? dense[t * cols + e] : 1.f;
+      uint4 raw = reinterpret_cast<uint4*>(act)[w];
+      __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(p[k]);
+        float a = moe_activation(f.x, gelu), b = moe_activation(f.y, gelu);
+        if (dense != nullptr) { a *= by; b *= by; }
+        p[k] = __floats2bfloat162_rn(a, b);
+      }
+      reinterpret_cast<uint4*>(act)[w] = raw;
+    }
+    return;
+  }
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = i / width;
     const int64_t c = i - t * width;
     const int e = c < (int64_t)experts * ff ? (int)(c / ff) : experts;
-    float x = to_f32(act[i]);
-    if (gelu == 1) x = 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
-    else if (gelu == 2) { x = fmaxf(x, 0.f); x *= x; }
+    float x = moe_activation(to_f32(act[i]), gelu);
     if (dense != nullptr) x *= dense[t * cols + e];
     act[i] = from_f32<T>(x);
   }
@@ -380,7 +405,8 @@ static int moe_scale_launch(void* act, const float* dense, int tokens, int exper
                 "moe_scale: bad sizes");
   if (tokens == 0) return VOSTI_OK;
   const int64_t n = (int64_t)tokens * ((int64_t)experts * ff + tail);
-  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  const int64_t items = (!is_f32 && ff % 8 == 0 && tail % 8 == 0) ? n / 8 : n;      // 16-byte words where the slices allow them
+  const int blocks = (int)((items + 255) / 256 < 148 * 16 ? (items + 255) / 256 : 148 * 16);
   if (is_f32) vosti_launch(moe_scale_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)act, dense, (int64_t)tokens, experts, ff, gelu, tail);
   else vosti_launch(moe_scale_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)act, dense, (int64_t)tokens, experts, ff, gelu, tail);
   VOSTI_LAUNCH_CHECK();
