@@ -160,10 +160,10 @@ __device__ __forceinline__ void warp_argmax(const float* v, const int* skip, int
 // Written: chosen and weights [tokens, top]; dense [tokens, dense_cols], zero but for the chosen
 // experts' weights (an identity expert has no column); ident [tokens], the sum of the chosen identity
 // experts' weights; and, with a gate row (the router's row number `routed`), its sigmoid in column
-// routed - identity of dense. One warp; lg holds the logits, sc / ch / gs / taken are scratch.
+// routed - identity of dense. One warp; lg holds the logits, sc / ch / gs / taken / picks are scratch.
 __device__ __forceinline__ void route_row_scored(const float* lg, int t, int routed, int identity, int top, const float* __restrict__ correction,
                                                  int groups, int keep, int gate_rows, float scale, float* sc, float* ch, float* gs,
-                                                 int* taken, int* __restrict__ chosen, float* __restrict__ weights,
+                                                 int* taken, int* picks, int* __restrict__ chosen, float* __restrict__ weights,
                                                  float* __restrict__ dense, float* __restrict__ ident, int dense_cols) {
   const int lane = threadIdx.x & 31;
   const int experts = routed - identity;
@@ -214,21 +214,24 @@ __device__ __forceinline__ void route_row_scored(const float* lg, int t, int rou
     __syncwarp();
     if (lane == 0) {
       ch[best_e] = -INFINITY;
-      chosen[(int64_t)t * top + r] = best_e;
+      picks[r] = best_e;
     }
     total += sc[best_e];
     __syncwarp();
   }
+  // a lane a pick: ids, weights, the dense row; the identity experts' share summed over the lanes
   const float inv = scale / (total + 1e-20f);
+  float own = 0.f;
+  for (int r = lane; r < top; r += 32) {
+    const int e = picks[r];
+    const float w = sc[e] * inv;
+    chosen[(int64_t)t * top + r] = e;
+    weights[(int64_t)t * top + r] = w;
+    if (e < experts) dense[(int64_t)t * dense_cols + e] = w;
+    else own += w;
+  }
+  own = warp_sum(own);
   if (lane == 0) {
-    float own = 0.f;
-    for (int r = 0; r < top; ++r) {
-      const int e = chosen[(int64_t)t * top + r];
-      const float w = sc[e] * inv;
-      weights[(int64_t)t * top + r] = w;
-      if (e < experts) dense[(int64_t)t * dense_cols + e] = w;
-      else own += w;
-    }
     if (ident != nullptr) ident[t] = own;
     if (gate_rows) dense[(int64_t)t * dense_cols + experts] = 1.f / (1.f + expf(-lg[routed]));
   }
@@ -236,12 +239,12 @@ __device__ __forceinline__ void route_row_scored(const float* lg, int t, int rou
 
 // Router product and scored choice in one kernel, one block per token (see route_row_scored). The
 // router's matrix is float32 [routed + gate_rows, k].
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 moe_router_scored_kernel(const void* __restrict__ x, int x_f32, const float* __restrict__ router, int routed, int identity, int k,
                          int top, const float* __restrict__ correction, int groups, int keep, int gate_rows, float scale,
                          int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ dense, float* __restrict__ ident,
                          int dense_cols, float* __restrict__ logits) {
-  extern __shared__ __align__(16) float router_smem[];   // [k] row, [rows] logits, [routed] scores, [routed] choice scores, [groups] x 2
+  extern __shared__ __align__(16) float router_smem[];   // [k] row, [rows] logits, [routed] scores, [routed] choice scores, [groups] x 2, [top] picks
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x, rows = routed + gate_rows;
@@ -251,9 +254,10 @@ moe_router_scored_kernel(const void* __restrict__ x, int x_f32, const float* __r
   float* ch = sc + routed;
   float* gs = ch + routed;
   int* taken = reinterpret_cast<int*>(gs + groups);
+  int* picks = taken + groups;
   router_logits(x, x_f32, router, rows, k, t, router_smem, lg, logits);
   if ((threadIdx.x >> 5) == 0)
-    route_row_scored(lg, t, routed, identity, top, correction, groups, keep, gate_rows, scale, sc, ch, gs, taken, chosen, weights,
+    route_row_scored(lg, t, routed, identity, top, correction, groups, keep, gate_rows, scale, sc, ch, gs, taken, picks, chosen, weights,
                      dense, ident, dense_cols);
 }
 
@@ -444,7 +448,7 @@ VOSTI_API int vosti_moe_router_scored(const void* x, int x_f32, const float* rou
   VOSTI_REQUIRE(groups >= 1 && routed % groups == 0 && keep >= 1 && keep <= groups, "moe_router: %d groups of which %d are kept do not divide %d experts", groups, keep, routed);
   VOSTI_REQUIRE(top > 0 && top <= (routed / groups) * keep, "moe_router: top %d exceeds the experts of the kept groups", top);
   VOSTI_REQUIRE(identity == 0 || ident != nullptr, "moe_router: identity experts need their output");
-  const size_t smem = (size_t)(((k + 3) & ~3) + routed + gate_rows + 2 * routed + 2 * groups) * sizeof(float);
+  const size_t smem = (size_t)(((k + 3) & ~3) + routed + gate_rows + 2 * routed + 2 * groups + top) * sizeof(float);
   VOSTI_REQUIRE(smem <= 200 * 1024, "moe_router: a row of %d elements does not fit shared memory", k);
   if (tokens == 0) return VOSTI_OK;
   {
@@ -454,7 +458,10 @@ VOSTI_API int vosti_moe_router_scored(const void* x, int x_f32, const float* rou
       configured = true;
     }
   }
-  vosti_launch(moe_router_scored_kernel, dim3(tokens), dim3(routed > 4 ? 256 : 128), smem, stream, x, x_f32, router, routed, identity, k, top,
+  // a warp a router row, so that all rows' products run side by side
+  const int rows = routed + gate_rows;
+  const int threads = rows >= 32 ? 1024 : (rows > 4 ? rows * 32 : 128);
+  vosti_launch(moe_router_scored_kernel, dim3(tokens), dim3(threads), smem, stream, x, x_f32, router, routed, identity, k, top,
                correction, groups, keep, gate_rows, scale, chosen, weights, dense, ident, routed - identity + gate_rows, logits);
   VOSTI_LAUNCH_CHECK();
 }
