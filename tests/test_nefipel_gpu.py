@@ -139,7 +139,7 @@ def test_gated_attention_mixer_against_plain(dtype, heads, kv, dk, dv, dims, sca
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv,dk,dv,dims,scaling,diff,page", [
     (3, 1, 10, 14, 6, YARN, 0.2, 8), (2, 2, 20, 8, 20, None, 0.45, 8), (1, 1, 2, 3, 2, YARN, 0.1, 4), (4, 2, 64, 64, 64, YARN, 0.3, 16),
-    (2, 1, 32, 96, 16, None, 0.25, 16), (8, 2, 48, 96, 48, dict(factor=4.0, original=64, fast=16.0, slow=2.0), 0.7, 8),
+    (2, 1, 32, 96, 16, None, 0.25, 16), (8, 2, 40, 88, 40, dict(factor=4.0, original=64, fast=16.0, slow=2.0), 0.7, 8),
     (2, 1, 128, 256, 64, None, 0.5, 16), (4, 2, 64, 128, 64, YARN, 0.3, 16), (2, 1, 128, 64, 32, None, 0.2, 16), (6, 2, 128, 128, 128, None, 0.4, 32),
     (2, 2, 64, 64, 16, None, 0.3, 8)])
 def test_differential_attention_mixer_against_plain(dtype, heads, kv, dk, dv, dims, scaling, diff, page):
@@ -243,7 +243,7 @@ def test_projection_post_pass_alone():
 
 # ---------------------------------------------------------------- feed-forwards
 @pytest.mark.parametrize("routed,identity,groups,keep,top,gate", [
-    (9, 3, 3, 2, 3, True), (5, 0, 1, 1, 2, False), (2, 1, 2, 1, 1, False), (16, 4, 4, 2, 4, True), (20, 4, 2, 1, 2, True),
+    (9, 3, 3, 2, 3, True), (5, 0, 1, 1, 2, False), (2, 1, 2, 1, 1, False), (16, 4, 4, 2, 4, True), (18, 6, 2, 1, 2, True),
     (64, 0, 8, 3, 6, False), (3, 0, 1, 1, 3, True), (40, 8, 40, 5, 5, False)])
 def test_scored_router_against_plain(routed, identity, groups, keep, top, gate):
     gen = torch.Generator().manual_seed(routed * 10 + top)

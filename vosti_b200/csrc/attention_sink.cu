@@ -9,7 +9,11 @@
 //   * a learned bias per (distance, head) added to the scaled score. The host hands a table
 //     bias[head][min(distance, last)] (already in base-2 units): beyond `last` the bias no
 //     longer changes, so the table is as long as the distances that differ;
-//   * a sink: one more term exp(sink[head]) in the softmax denominator, with no key or value.
+//   * a sink: one more term exp(sink[head]) in the softmax denominator, with no key or value;
+//   * two score maps a head over the same values (differential attention), combined after the
+//     softmax, and a finish of the head's output: unit root mean square, a sigmoid gate (HeadFinish);
+//   * a projection post-pass by heads (qkv_heads): bias, per-head RMS norm with a shared weight,
+//     rotation in pairs (i, i + n / 2) or (2i, 2i + 1), from a float32 product or its unsummed K splits.
 //
 // Kernels: the projection's post-pass (temperature, keys and values into their cache slots)
 // and the attention itself on the CUDA cores, one warp per (query token, query head), float32

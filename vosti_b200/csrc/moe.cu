@@ -7,6 +7,11 @@
 // choice twice: as lists (expert ids and weights, [tokens, top]) and as a dense float32 matrix
 // [tokens, experts] that is zero where an expert was not chosen.
 //
+// moe_router_scored: another way to choose (route_row_scored): softmax scores over all routed rows,
+// the choice by score + correction inside the best groups of neighbouring rows, rows at the end
+// that stand for experts returning their input, and one more router row whose sigmoid gates a
+// shared expert. moe_identity adds the input-returning experts' share of the input.
+//
 // moe_scale: multiplies each expert's slice of the stacked activation [tokens, experts * ff] by
 // the token's weight for that expert (zero for experts it did not choose), after an optional
 // activation of its own (the exact GELU, for experts without a gate), so that one product

@@ -1,4 +1,5 @@
-// Row-wise kernels: embedding gather, (residual-fused) RMSNorm, SiLU(gate)*up.
+// Row-wise kernels: embedding gather (also as the float32 start of a residual stream),
+// (residual-fused) RMSNorm, SiLU(gate)*up and its relu variants.
 // Formulas as the reference computes them: kernels/triton_kernels/embedding.py:62-84,
 // rmsnorm.py:63-93, rmsnorm_residual.py:86-125, silu_mul.py:66-87. All arithmetic in
 // float32; T is the storage type of activations (float or bf16).

@@ -2,8 +2,9 @@
 // type: the deferred residual sum, Dynamic Tanh (a norm without statistics), the packing of
 // [stream ; first embedding] for a loop's re-entry product, and the merge of side-by-side
 // mixer branches (each divided by its root mean square, weighted, averaged; or a plain sum with a
-// constant per branch), and the root-mean-square norm over the stream (weight stored as it is
-// or around zero).
+// constant per branch), the root-mean-square norm over the stream (weight stored as it is
+// or around zero), and the norm after the sum of blocks that norm what they have added
+// (y = rms(alpha * stream + terms) * w becomes the stream).
 //
 // The stream is float32 [rows, width]. A sublayer's output ("term") is float32 or the serving
 // type; up to two terms wait to be added (mixer and feed-forward of a parallel block), and the
