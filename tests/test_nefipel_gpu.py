@@ -313,15 +313,22 @@ def test_feed_forwards_against_plain(dtype, mlp):
     if mlp["kind"] == "moe":
         W["router"] = (3.0 * W["router"]).to(torch.bfloat16).float()          # decided choices: bfloat16 inputs must not flip them
     give(part, W, dtype)
-    x = rounded(tokens, width, gen=gen)
     fn = plain.dense_feed_forward if mlp["kind"] == "dense" else (lambda h, w: plain.expert_feed_forward(h, w, mlp))
-    want = fn(x.double(), {k: v.double() for k, v in W.items()}).float()
-    got = ops.materialize(part.forward(Ctx(dtype), x.to(DEV, dtype))).float().cpu()
-    assert got.dtype == torch.float32
-    if dtype == torch.float32:
-        assert torch.allclose(got, want, atol=1e-3, rtol=3e-4), float((got - want).abs().max())
-    else:
-        assert float((got - want).abs().mean() / want.abs().mean()) < 0.02
+    # a step of few tokens (all experts side by side in one product) and a long portion (rows sorted by expert,
+    # here also for few experts a pick)
+    part.GROUPED_MIN_RATIO = 0
+    for tokens in (90, 300):
+        x = rounded(tokens, width, gen=gen)
+        want = fn(x.double(), {k: v.double() for k, v in W.items()}).float()
+        got = ops.materialize(part.forward(Ctx(dtype), x.to(DEV, dtype))).float().cpu()
+        assert got.dtype == torch.float32
+        if dtype == torch.float32:
+            assert torch.allclose(got, want, atol=1e-3, rtol=3e-4), (tokens, float((got - want).abs().max()))
+        else:
+            assert float((got - want).abs().mean() / want.abs().mean()) < 0.02, tokens
+    if mlp["kind"] == "moe":
+        routed = mlp["router"]["experts"] + (mlp["router"].get("identity") or 0)
+        assert bool(part.per_expert) == (mlp["router"]["top"] < routed)
 
 
 # ---------------------------------------------------------------- whole models
